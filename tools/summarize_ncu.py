@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Turn the outputs of tools/ncu_bench.sh (gpurun_out/launches_<tag>.csv, gpurun_out/step_<tag>_full.ncu-rep and, when
 present, batch_<tag>_full.ncu-rep / gemm_<tag>_full.ncu-rep) into the committed summaries under profiles/: the launch list
-(shares), the metrics of the full captures, the executed-instruction and stall-sample shares per source function, and
+(shares), the metrics of the full captures and
 step_kernel_traffic.json (read by bench.py for roofline.traffic).
 
     python tools/summarize_ncu.py [--tag r2]
@@ -11,7 +11,6 @@ import collections
 import csv
 import json
 import os
-import re
 import subprocess
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -84,76 +83,12 @@ def full_capture(tag):
             lines.append(f"{h:80s} {kv[h][1]:>16s} {kv[h][0]}")
     rd = float(kv["dram__bytes_read.sum"][1]) * TO_BYTES[kv["dram__bytes_read.sum"][0]]
     wr = float(kv["dram__bytes_write.sum"][1]) * TO_BYTES[kv["dram__bytes_write.sum"][0]]
-    # executed instructions / stall samples per source function (needs the same build in-tree for the line table)
-    src = subprocess.run(["ncu", "-i", rep, "--page", "source", "--csv"], capture_output=True, text=True).stdout
-    srows = list(csv.reader(src.splitlines()))
-    sh = srows[1]
-    ia, iex, ismp = sh.index("Address"), sh.index("Instructions Executed"), sh.index("# Samples")
-    data = [(int(r[ia], 16), int(r[iex]), int(r[ismp])) for r in srows[2:] if len(r) > iex and r[iex].isdigit()]
-    try:
-        off2line = line_table()
-        cu = open(os.path.join(REPO, "dia_tts_prune_b200", "csrc", "step_kernel.cu")).read().split("\n")
-        starts = []
-        for i, l in enumerate(cu, 1):
-            m = re.match(r"(?:static )?(?:template.*)?__device__.*?(\w+)\(", l)
-            if m and not l.startswith(" "):
-                starts.append((i, m.group(1)))
-            if l.startswith('extern "C" __global__'):
-                starts.append((i, "kernel body"))
-
-        def bucket(k):
-            if k is None:
-                return "?"
-            f, ln = k
-            if f != "step_kernel.cu":
-                return f
-            name = "?"
-            for s, n in starts:
-                if s <= ln:
-                    name = n
-            return name
-        ex, sm = collections.Counter(), collections.Counter()
-        for a, e, n in data:
-            b = bucket(off2line.get(a - data[0][0]))
-            ex[b] += e
-            sm[b] += n
-        te, ts = sum(ex.values()), sum(sm.values())
-        lines.append("# share of executed warp instructions / of stall samples per source function (inlined code is "
-                     "attributed to the function it was written in)")
-        for k, v in ex.most_common(12):
-            lines.append(f"{100 * v / te:6.1f}% executed {100 * sm[k] / ts:6.1f}% samples   {k}")
-    except Exception as e:                                      # pragma: no cover
-        lines.append(f"# (no per-function table: {e})")
     with open(os.path.join(PROF, f"{tag}_ncu_step_kernel_full.txt"), "w") as f:
         f.write("\n".join(lines) + "\n")
     with open(os.path.join(PROF, "step_kernel_traffic.json"), "w") as f:
         json.dump({"dram_bytes_per_step": (rd + wr) / 64, "captured_steps_per_launch": 64, "first_slot": 1500,
                    "source": f"profiles/{tag}_ncu_step_kernel_full.txt"}, f)
         f.write("\n")
-
-
-def line_table():
-    import tempfile
-    lib = os.path.join(REPO, "dia_tts_prune_b200", "csrc", "libdia_b200.so")
-    with tempfile.TemporaryDirectory() as d:
-        subprocess.run(["cuobjdump", "-xelf", "all", lib], cwd=d, capture_output=True)
-        cub = [f for f in os.listdir(d) if f.startswith("step_kernel.")][0]
-        txt = subprocess.run(["nvdisasm", "-g", "-c", os.path.join(d, cub)], capture_output=True, text=True).stdout
-    cur, infn, out = None, False, {}
-    for line in txt.splitlines():
-        if re.match(r"\s*\.text\.dia_step_kernel:", line):
-            infn = True
-            continue
-        if re.match(r"\s*\.text\.", line):
-            infn = False
-        m = re.search(r'//## File "([^"]+)", line (\d+)', line)
-        if m:
-            cur = (m.group(1).split("/")[-1], int(m.group(2)))
-            continue
-        m = re.match(r"\s+/\*([0-9a-f]{4,})\*/\s+\S", line)
-        if infn and m:
-            out[int(m.group(1), 16)] = cur
-    return out
 
 
 if __name__ == "__main__":
