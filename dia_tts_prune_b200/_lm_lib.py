@@ -1,0 +1,98 @@
+"""ctypes bindings of the C ABI in ``include/lm_b200.h`` (``csrc/liblm_b200.so``).
+
+Like ``_lib.py`` there is no fallback: a missing library is built with nvcc on first use, and a failing call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+from . import build as _build
+
+MIXER_SINK_ATTENTION = 1
+FF_NONE, FF_ROUTED_EXPERTS = 0, 1
+E_OK, E_INVAL, E_CUDA, E_NOMEM, E_UNSUPPORTED = 0, -1, -2, -3, -5
+
+_vp, _i, _f = C.c_void_p, C.c_int32, C.c_float
+
+
+class Norm(C.Structure):
+    _fields_ = [("w", _vp), ("b", _vp), ("alpha", _f), ("reserved", _i)]
+
+
+class Layer(C.Structure):
+    _fields_ = [("mixer", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("window", _i), ("keep_first", _i),
+                ("scale", _f), ("softcap", _f), ("ff", _i), ("experts", _i), ("top", _i), ("expert_ff", _i),
+                ("shared_ff", _i), ("norm_mix_in", Norm), ("norm_mix_out", Norm), ("norm_ff_in", Norm), ("norm_ff_out", Norm),
+                ("tap_mix", _vp), ("tap_ff", _vp), ("w_qk", _vp), ("q_norm", _vp), ("k_norm", _vp), ("temp", _vp),
+                ("slopes", _vp), ("sink", _vp), ("w_o", _vp), ("w_router", _vp), ("w_gate_up", _vp), ("w_down", _vp),
+                ("ws_gate_up", _vp), ("ws_down", _vp), ("k_pages", _vp), ("v_pages", _vp), ("tail_mix", _vp), ("tail_ff", _vp)]
+
+
+class Model(C.Structure):
+    _fields_ = [("n_layer", _i), ("width", _i), ("vocab", _i), ("taps", _i), ("page_size", _i), ("max_pages", _i),
+                ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("reserved", _i), ("embed", _vp), ("head", _vp),
+                ("final_norm", Norm), ("page_table", _vp)]
+
+
+_ci = C.c_int
+_SIGNATURES = {
+    "lm_b200_abi_version": (_ci, []),
+    "lm_b200_last_cuda_error": (C.c_char_p, []),
+    "lm_b200_launch_count": (C.c_int64, []),
+    "lm_b200_engine_create": (_ci, [C.POINTER(Model), C.POINTER(Layer), _ci, C.POINTER(_vp)]),
+    "lm_b200_engine_destroy": (_ci, [_vp]),
+    "lm_b200_engine_workspace_bytes": (C.c_size_t, [_vp]),
+    "lm_b200_forward": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp]),
+    "lm_b200_op_norm_tapmix": (_ci, [_vp, _ci, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
+    "lm_b200_op_mixer": (_ci, [_vp, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
+    "lm_b200_op_ff": (_ci, [_vp, _ci, _vp, _ci, _vp, _vp]),
+    "lm_b200_op_linear": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "lm_b200_argmax_rows": (_ci, [_vp, _ci, _ci, _vp, _vp]),
+}
+
+_lib = None
+
+
+def header_symbols() -> list[str]:
+    text = (Path(_build.INCLUDE) / "lm_b200.h").read_text()
+    return sorted(set(re.findall(r"\b(lm_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def load(build_if_missing: bool = True) -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LM_LIB
+    if build_if_missing and _build.is_stale("lm"):
+        try:
+            _build.build(target="lm")
+        except Exception as e:
+            if not path.exists():
+                raise RuntimeError(f"liblm_b200.so is missing and could not be built: {e}") from e
+    if not path.exists():
+        raise RuntimeError(f"{path} not found: run `python -m dia_tts_prune_b200.build lm` (there is no CPU fallback)")
+    lib = C.CDLL(str(path))
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    if lib.lm_b200_abi_version() != 1:
+        raise RuntimeError("liblm_b200.so ABI version mismatch")
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc == 0:
+        return
+    msg = {E_INVAL: "invalid argument", E_CUDA: "CUDA error", E_NOMEM: "out of memory",
+           E_UNSUPPORTED: "not supported on this path"}.get(rc, f"error {rc}")
+    if rc == E_CUDA:
+        msg += f" [{load().lm_b200_last_cuda_error().decode()}]"
+    if rc == E_UNSUPPORTED:
+        raise NotImplementedError(f"{what}: {msg}")
+    if rc == E_INVAL:
+        raise ValueError(f"{what}: {msg}")
+    raise RuntimeError(f"{what}: {msg}")

@@ -1,0 +1,312 @@
+// lm_engine.cu - the C ABI of include/lm_b200.h: descriptor checks, the step workspace, and the launch sequence of one step.
+//
+// One step = embed, then per layer
+//   h = tapmix(norm(x))                         dyt_tapmix (+ tail update)
+//   [q | k] = h W_qk^T                          linear
+//   q, k norms; k -> key pages, raw k -> value pages   qk_norm_cache
+//   attention over the pages                    sink_attention
+//   y = o W_o^T;  x += norm(y)                  linear, residual_dyt
+//   h = tapmix'(norm'(x))                       dyt_tapmix (+ tail update)
+//   z = h W_router^T; top experts; groups       linear, router_topk, moe_group
+//   experts on score * h (grouped by expert)    linear (gate | up), silu_mul, linear (down)
+//   the shared expert on h                      linear, silu_mul, linear
+//   x += norm(shared + the row's expert rows)   residual_dyt
+// and the final norm + head on the wanted rows.  Nothing here depends on how many sequences the rows belong to.
+#include <algorithm>
+#include <atomic>
+#include <cstdio>
+#include <new>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "lm_b200.h"
+#include "lm_internal.h"
+
+namespace {
+
+std::atomic<long long> g_launches{0};
+thread_local char g_cuda_err[256] = "";
+
+struct Guard {                                   // run on the engine's device, restore the caller's
+    int prev = -1;
+    bool ok = true;
+    explicit Guard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~Guard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+inline int cuda_fail(cudaError_t e) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return e == cudaErrorNotSupported ? LM_B200_EUNSUPPORTED : LM_B200_ECUDA;
+}
+
+#define LCK(call)                                       \
+    do {                                                \
+        cudaError_t e__ = (call);                       \
+        if (e__ != cudaSuccess) return cuda_fail(e__);  \
+        g_launches++;                                   \
+    } while (0)
+
+inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline lm::NormW N(const lm_b200_norm& n) { return lm::NormW{n.w, n.b, n.alpha}; }
+
+}  // namespace
+
+struct lm_b200_engine {
+    lm_b200_model m;
+    std::vector<lm_b200_layer> layers;
+    int device = 0;
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    int max_slots = 0;                           // assignment slots of the widest expert layer
+    // workspace (fp32 unless noted)
+    float *x, *h, *qk, *att, *y, *z, *sel_w, *a_scale, *gu, *mid, *parts, *sgu, *smid, *hw;
+    int *sel_e, *slot_of, *a_row, *a_expert, *n_slots;
+};
+
+namespace {
+
+int slots_bound(int rows, int top, int experts) {
+    const int n = rows * top;
+    if (n <= lm::kRowsKernelMax) return n;
+    return n + std::min(experts, n) * (lm::kTileRows - 1);
+}
+
+struct StepView {
+    const int *token, *want;
+    lm::RowMeta rm;
+    lm::SeqMeta sm;
+};
+StepView view(const int32_t* step, int M, int n_seq) {
+    StepView v;
+    v.token = step;
+    v.rm = lm::RowMeta{step + M, step + 2 * (size_t)M, step + 3 * (size_t)M};
+    const int32_t* s = step + 4 * (size_t)M;
+    v.sm = lm::SeqMeta{s, s + n_seq, s + 2 * (size_t)n_seq};
+    v.want = s + 3 * (size_t)n_seq;
+    return v;
+}
+
+int check_layer(const lm_b200_model& m, const lm_b200_layer& l) {
+    if (l.mixer != LM_B200_MIXER_SINK_ATTENTION) return LM_B200_EUNSUPPORTED;
+    if (l.heads <= 0 || l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.dim > 256) return LM_B200_EINVAL;
+    if (!l.w_qk || !l.q_norm || !l.k_norm || !l.w_o || !l.k_pages || !l.v_pages) return LM_B200_EINVAL;
+    if (!l.norm_mix_in.w || !l.norm_mix_in.b || !l.norm_mix_out.w || !l.norm_mix_out.b) return LM_B200_EINVAL;
+    if (m.taps > 1 && ((l.tap_mix && !l.tail_mix) || (l.tap_ff && !l.tail_ff))) return LM_B200_EINVAL;
+    if (l.ff == LM_B200_FF_NONE) return LM_B200_OK;
+    if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EUNSUPPORTED;
+    if (l.experts <= 0 || l.top <= 0 || l.top > l.experts || l.expert_ff <= 0 || l.shared_ff < 0) return LM_B200_EINVAL;
+    if (!l.w_router || !l.w_gate_up || !l.w_down || (l.shared_ff > 0 && (!l.ws_gate_up || !l.ws_down))) return LM_B200_EINVAL;
+    if (!l.norm_ff_in.w || !l.norm_ff_in.b || !l.norm_ff_out.w || !l.norm_ff_out.b) return LM_B200_EINVAL;
+    if (3 * (size_t)l.experts * sizeof(int) > 40000) return LM_B200_EUNSUPPORTED;
+    return LM_B200_OK;
+}
+
+// h = tapmix(norm(x)) and the tail of every scheduled sequence
+int norm_tapmix(lm_b200_engine* e, const lm_b200_layer& l, int sub, const float* x, const StepView& v, int M, int n_seq,
+                float* out, cudaStream_t st) {
+    const lm_b200_norm& n = sub ? l.norm_ff_in : l.norm_mix_in;
+    const float* taps = sub ? l.tap_ff : l.tap_mix;
+    float* tail = sub ? l.tail_ff : l.tail_mix;
+    const int T = taps ? e->m.taps : 0;
+    LCK(lm::launch_dyt_tapmix(x, N(n), taps, T, tail, v.rm, out, M, e->m.width, st));
+    if (T > 1) LCK(lm::launch_tapmix_tail(x, N(n), T, tail, v.sm, n_seq, e->m.width, st));
+    return LM_B200_OK;
+}
+
+int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const StepView& v, int M, float* y, cudaStream_t st) {
+    const int D = e->m.width, nq = l.heads * l.dim, nk = l.kv_heads * l.dim;
+    const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
+    LCK(lm::launch_linear(h, D, l.w_qk, 0, e->qk, nq + nk, M, nq + nk, D, nullptr, st));
+    LCK(lm::launch_qk_norm_cache(e->qk, nq, nk, l.q_norm, l.k_norm, e->m.eps, l.k_pages, l.v_pages, pm, l.kv_heads, l.dim,
+                                 v.rm, M, st));
+    const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
+    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, M, st));
+    LCK(lm::launch_linear(e->att, nq, l.w_o, 0, y, D, M, D, nq, nullptr, st));
+    return LM_B200_OK;
+}
+
+// leaves the shared expert's rows in e->y (when there is one) and the experts' rows in e->parts / e->slot_of
+int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, int M, cudaStream_t st) {
+    const int D = e->m.width, E = l.experts, top = l.top, F = l.expert_ff, Sf = l.shared_ff;
+    LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, E, M, E, D, nullptr, st));
+    LCK(lm::launch_router_topk(e->z, E, top, M, e->sel_e, e->sel_w, st));
+    const int n_assign = M * top, bound = slots_bound(M, top, E);
+    const int pad = n_assign <= lm::kRowsKernelMax ? 1 : lm::kTileRows;
+    const lm::GroupMap gm{e->a_row, e->a_scale, e->a_expert, e->n_slots};
+    LCK(lm::launch_moe_group(e->sel_e, e->sel_w, n_assign, top, E, pad, gm, e->slot_of, bound, st));
+    LCK(lm::launch_linear(h, D, l.w_gate_up, 2LL * F * D, e->gu, 2 * F, bound, 2 * F, D, &gm, st));
+    LCK(lm::launch_silu_mul(e->gu, e->mid, bound, F, &gm, st));
+    // the rows of mid are already in slot order: identity gather, no scale, the slots' experts
+    const lm::GroupMap gm_down{nullptr, nullptr, e->a_expert, e->n_slots};
+    LCK(lm::launch_linear(e->mid, F, l.w_down, (long long)D * F, e->parts, D, bound, D, F, &gm_down, st));
+    if (Sf > 0) {
+        LCK(lm::launch_linear(h, D, l.ws_gate_up, 0, e->sgu, 2 * Sf, M, 2 * Sf, D, nullptr, st));
+        LCK(lm::launch_silu_mul(e->sgu, e->smid, M, Sf, nullptr, st));
+        LCK(lm::launch_linear(e->smid, Sf, l.ws_down, 0, e->y, D, M, D, Sf, nullptr, st));
+    }
+    return LM_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lm_b200_abi_version(void) { return LM_B200_ABI_VERSION; }
+const char* lm_b200_last_cuda_error(void) { return g_cuda_err; }
+int64_t lm_b200_launch_count(void) { return g_launches.load(); }
+
+int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layers, int device, lm_b200_engine** out) {
+    if (!model || !layers || !out) return LM_B200_EINVAL;
+    const lm_b200_model& m = *model;
+    if (m.n_layer <= 0 || m.width <= 0 || m.vocab <= 0 || m.taps < 0 || m.taps > lm::kMaxTaps || m.page_size <= 0 ||
+        m.max_pages <= 0 || m.n_slots <= 0 || m.max_rows <= 0 || !m.embed || !m.head || !m.final_norm.w || !m.final_norm.b ||
+        !m.page_table)
+        return LM_B200_EINVAL;
+    for (int i = 0; i < m.n_layer; ++i) {
+        const int rc = check_layer(m, layers[i]);
+        if (rc != LM_B200_OK) return rc;
+    }
+    Guard g(device);
+    if (!g.ok) return LM_B200_ECUDA;
+    lm_b200_engine* e = new (std::nothrow) lm_b200_engine();
+    if (!e) return LM_B200_ENOMEM;
+    e->m = m;
+    e->layers.assign(layers, layers + m.n_layer);
+    e->device = device;
+    const size_t R = (size_t)m.max_rows, D = (size_t)m.width;
+    size_t qk = 0, att = 0, E = 1, top = 1, F = 1, Sf = 1, slots = 1;
+    for (const lm_b200_layer& l : e->layers) {
+        qk = std::max(qk, (size_t)(l.heads + l.kv_heads) * l.dim);
+        att = std::max(att, (size_t)l.heads * l.dim);
+        if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
+            E = std::max(E, (size_t)l.experts);
+            top = std::max(top, (size_t)l.top);
+            F = std::max(F, (size_t)l.expert_ff);
+            Sf = std::max(Sf, (size_t)l.shared_ff);
+            slots = std::max(slots, (size_t)slots_bound(m.max_rows, l.top, l.experts));
+        }
+    }
+    e->max_slots = (int)slots;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t at = off; off += (bytes + 255) & ~(size_t)255; return at; };
+    const size_t o_x = take(R * D * 4), o_h = take(R * D * 4), o_qk = take(R * qk * 4), o_att = take(R * att * 4),
+                 o_y = take(R * D * 4), o_z = take(R * E * 4), o_sel_w = take(R * top * 4), o_sel_e = take(R * top * 4),
+                 o_slot_of = take(R * top * 4), o_a_row = take(slots * 4), o_a_scale = take(slots * 4),
+                 o_a_expert = take(slots * 4), o_n_slots = take(4), o_gu = take(slots * 2 * F * 4), o_mid = take(slots * F * 4),
+                 o_parts = take(slots * D * 4), o_sgu = take(R * 2 * Sf * 4), o_smid = take(R * Sf * 4), o_hw = take(R * D * 4);
+    if (cudaMalloc(&e->arena, off) != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete e;
+        return LM_B200_ENOMEM;
+    }
+    e->arena_bytes = off;
+    char* b = e->arena;
+    e->x = (float*)(b + o_x); e->h = (float*)(b + o_h); e->qk = (float*)(b + o_qk); e->att = (float*)(b + o_att);
+    e->y = (float*)(b + o_y); e->z = (float*)(b + o_z); e->sel_w = (float*)(b + o_sel_w); e->sel_e = (int*)(b + o_sel_e);
+    e->slot_of = (int*)(b + o_slot_of); e->a_row = (int*)(b + o_a_row); e->a_scale = (float*)(b + o_a_scale);
+    e->a_expert = (int*)(b + o_a_expert); e->n_slots = (int*)(b + o_n_slots); e->gu = (float*)(b + o_gu);
+    e->mid = (float*)(b + o_mid); e->parts = (float*)(b + o_parts); e->sgu = (float*)(b + o_sgu);
+    e->smid = (float*)(b + o_smid); e->hw = (float*)(b + o_hw);
+    *out = e;
+    return LM_B200_OK;
+}
+
+int lm_b200_engine_destroy(lm_b200_engine* e) {
+    if (!e) return LM_B200_OK;
+    Guard g(e->device);
+    if (e->arena) cudaFree(e->arena);
+    delete e;
+    return LM_B200_OK;
+}
+
+size_t lm_b200_engine_workspace_bytes(const lm_b200_engine* e) { return e ? e->arena_bytes : 0; }
+
+int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_want, float* logits_out, float* layers_out,
+                    void* stream) {
+    if (!e || !step || M <= 0 || M > e->m.max_rows || n_seq <= 0 || n_seq > M || n_want < 0 || n_want > M ||
+        (n_want > 0 && !logits_out))
+        return LM_B200_EINVAL;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    cudaStream_t st = S(stream);
+    const StepView v = view(step, M, n_seq);
+    const int D = e->m.width;
+    LCK(lm::launch_embed(e->m.embed, v.token, e->x, M, e->m.vocab, D, st));
+    for (int i = 0; i < e->m.n_layer; ++i) {
+        const lm_b200_layer& l = e->layers[i];
+        int rc = norm_tapmix(e, l, 0, e->x, v, M, n_seq, e->h, st);
+        if (rc) return rc;
+        rc = mixer(e, l, e->h, v, M, e->y, st);
+        if (rc) return rc;
+        LCK(lm::launch_residual_dyt(e->x, e->y, nullptr, nullptr, 0, N(l.norm_mix_out), M, D, st));
+        if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
+            rc = norm_tapmix(e, l, 1, e->x, v, M, n_seq, e->h, st);
+            if (rc) return rc;
+            rc = feed_forward(e, l, e->h, M, st);
+            if (rc) return rc;
+            LCK(lm::launch_residual_dyt(e->x, l.shared_ff > 0 ? e->y : nullptr, e->parts, e->slot_of, l.top, N(l.norm_ff_out), M,
+                                        D, st));
+        }
+        if (layers_out) {
+            if (cudaMemcpyAsync(layers_out + (size_t)i * M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, st) !=
+                cudaSuccess)
+                return cuda_fail(cudaGetLastError());
+        }
+    }
+    if (n_want > 0) {
+        LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, n_want, D, st));
+        LCK(lm::launch_linear(e->hw, D, e->m.head, 0, logits_out, e->m.vocab, n_want, e->m.vocab, D, nullptr, st));
+    }
+    return LM_B200_OK;
+}
+
+int lm_b200_op_norm_tapmix(lm_b200_engine* e, int layer, int sub, const float* x, const int32_t* step, int M, int n_seq,
+                           float* out, void* stream) {
+    if (!e || layer < 0 || layer >= e->m.n_layer || (sub != 0 && sub != 1) || !x || !step || !out || M <= 0 ||
+        M > e->m.max_rows || n_seq <= 0)
+        return LM_B200_EINVAL;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    return norm_tapmix(e, e->layers[layer], sub, x, view(step, M, n_seq), M, n_seq, out, S(stream));
+}
+
+int lm_b200_op_mixer(lm_b200_engine* e, int layer, const float* h, const int32_t* step, int M, int n_seq, float* y,
+                     void* stream) {
+    if (!e || layer < 0 || layer >= e->m.n_layer || !h || !step || !y || M <= 0 || M > e->m.max_rows || n_seq <= 0)
+        return LM_B200_EINVAL;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    return mixer(e, e->layers[layer], h, view(step, M, n_seq), M, y, S(stream));
+}
+
+int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y, void* stream) {
+    if (!e || layer < 0 || layer >= e->m.n_layer || !h || !y || M <= 0 || M > e->m.max_rows) return LM_B200_EINVAL;
+    const lm_b200_layer& l = e->layers[layer];
+    if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    const int rc = feed_forward(e, l, h, M, S(stream));
+    if (rc) return rc;
+    const lm::NormW none{nullptr, nullptr, 0.f};                  // plain sum, written to y
+    LCK(lm::launch_residual_dyt(y, l.shared_ff > 0 ? e->y : nullptr, e->parts, e->slot_of, l.top, none, M, e->m.width, S(stream)));
+    return LM_B200_OK;
+}
+
+int lm_b200_op_linear(const float* A, const void* W_bf16, float* Y, int M, int N, int K, void* stream) {
+    if (!A || !W_bf16 || !Y || M <= 0 || N <= 0 || K <= 0) return LM_B200_EINVAL;
+    LCK(lm::launch_linear(A, K, W_bf16, 0, Y, N, M, N, K, nullptr, S(stream)));
+    return LM_B200_OK;
+}
+
+int lm_b200_argmax_rows(const float* logits, int M, int V, int32_t* out, void* stream) {
+    if (!logits || !out || M <= 0 || V <= 0) return LM_B200_EINVAL;
+    LCK(lm::launch_argmax_rows(logits, M, V, out, S(stream)));
+    return LM_B200_OK;
+}
+
+}  // extern "C"

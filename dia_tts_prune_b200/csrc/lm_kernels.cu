@@ -1,0 +1,610 @@
+// lm_kernels.cu - row kernels of the decoder-only language-model path (sm_100a).
+//
+// A step of the language-model engine is a flat batch of M rows: the new tokens of every scheduled sequence, one row per
+// token, each row carrying (sequence slot, position, position of the first row its sequence has in this step).  Prompt
+// portions, single decoded tokens and mixed batches are the same launch sequence.  Every kernel here computes a row's
+// result from that row (and the sequence state it points at) alone, in an order of operations that does not depend on
+// which other rows are in the batch - so the value at a position is bit-identical however the prompt was cut.
+//
+// Precision: activations, the residual stream, norms, router, attention scores / weights and the K/V pages are fp32;
+// matrices are bf16 in memory and multiplied with fp32 accumulation.
+//
+//   embed_rows_bf16_kernel     token rows of a bf16 table
+//   dyt_tapmix_kernel          DynamicTanh norm fused with the causal per-channel tap mix (short convolution over time,
+//                              identity added), previous inputs from the step itself or from the sequence's tail state
+//   tapmix_tail_kernel         keeps the last taps-1 normed inputs of every scheduled sequence
+//   linear_tile_kernel         Y = A . W^T, 64 x 64 x 16 tiles of fp32 FMAs, optional row gather / scale / per-tile expert
+//   linear_rows_kernel         the same contract for a handful of rows: one warp per output element
+//   qk_norm_cache_kernel       whole-projection RMS norm of q and k, raw k and normed k scattered into the paged cache
+//   sink_attention_kernel      softmax attention over the pages with per-head temperature, tanh cap, linear distance
+//                              bias, a window that keeps the first tokens, and a value-less sink term in the denominator
+//   router_topk_kernel         sigmoid scores and the `top` best experts of every row
+//   moe_group_kernel           groups (row, expert) assignments by expert, padded to the GEMM's row tile
+//   silu_mul_kernel            silu(gate) * up on [gate | up] rows
+//   residual_dyt_kernel        x += DynamicTanh(y [+ the row's expert outputs])
+//   dyt_gather_kernel          DynamicTanh of selected rows (the rows whose logits are wanted)
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "lm_internal.h"
+
+namespace lm {
+
+namespace {
+
+__device__ __forceinline__ float bf(const __nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ float dyt(float x, float alpha, float w, float b) { return fmaf(tanhf(alpha * x), w, b); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// fixed-tree block reductions (red: one float per warp); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; ++i) t += red[i];
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float t = -CUDART_INF_F;
+    for (int i = 0; i < nw; ++i) t = fmaxf(t, red[i]);
+    return t;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void embed_rows_bf16_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
+                                       float* __restrict__ out, int V, int D) {
+    const int r = blockIdx.x;
+    const int id = ids[r];
+    const bool ok = id >= 0 && id < V;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) out[(size_t)r * D + c] = ok ? bf(table[(size_t)id * D + c]) : 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// out[r][c] = n_r[c] + sum_j cw[c][j] * n_{r - (taps-1-j)}[c],  n = DynamicTanh(x) of the same sequence, zero before its
+// start.  Positions before this step's first row of the sequence come from tail[slot][i] (position start - (taps-1) + i).
+__global__ void dyt_tapmix_kernel(const float* __restrict__ x, const float* __restrict__ nw, const float* __restrict__ nb,
+                                  float alpha, const float* __restrict__ cw, int taps, const float* __restrict__ tail,
+                                  const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                                  const int* __restrict__ row_start, float* __restrict__ out, int D) {
+    const int r = blockIdx.x;
+    const int slot = row_slot[r], pos = row_pos[r], start = row_start[r];
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
+        const float w = nw[c], b = nb[c];
+        const float cur = dyt(x[(size_t)r * D + c], alpha, w, b);
+        float acc = cur;
+        if (taps > 0) acc = fmaf(cw[(size_t)c * taps + taps - 1], cur, acc);
+        for (int o = 1; o < taps; ++o) {
+            const int p = pos - o;
+            if (p < 0) break;
+            float v;
+            if (p >= start) v = dyt(x[(size_t)(r - o) * D + c], alpha, w, b);
+            else v = tail[((size_t)slot * (taps - 1) + (p - (start - (taps - 1)))) * D + c];
+            acc = fmaf(cw[(size_t)c * taps + taps - 1 - o], v, acc);
+        }
+        out[(size_t)r * D + c] = acc;
+    }
+}
+
+// tail[slot][i] <- normed input at position (start + count) - (taps-1) + i, for every scheduled sequence s:
+// from this step's rows when that position is in the step, else the old tail shifted by `count`.
+__global__ void tapmix_tail_kernel(const float* __restrict__ x, const float* __restrict__ nw, const float* __restrict__ nb,
+                                   float alpha, int taps, float* __restrict__ tail, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ seq_row0, const int* __restrict__ seq_count, int D) {
+    const int s = blockIdx.x, T1 = taps - 1;
+    const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s];
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
+        float keep[kMaxTaps];
+        float* t = tail + (size_t)slot * T1 * D + c;
+#pragma unroll
+        for (int i = 0; i < kMaxTaps; ++i) {
+            if (i >= T1) break;
+            const int q = n - T1 + i;                             // row of the step, if >= 0
+            if (q >= 0) keep[i] = dyt(x[(size_t)(row0 + q) * D + c], alpha, nw[c], nb[c]);
+            else keep[i] = t[(size_t)(i + n) * D];                // old tail entry i + n  (< T1 because q < 0)
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxTaps; ++i) {
+            if (i >= T1) break;
+            t[(size_t)i * D] = keep[i];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Y[a][n] = sum_k scale_a * A[src_a][k] * W_e[n][k].  Without the maps: src_a = a, scale 1, expert 0.  With them
+// (expert groups): a indexes padded assignment slots, a_row[a] < 0 is padding, the expert of a tile is a_expert of its
+// first slot.  n_slots (device) bounds the slots in use; the grid covers the host's upper bound.
+constexpr int BM = 64, BN = 64, BK = 16;
+
+__global__ void __launch_bounds__(256)
+linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
+                   float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
+                   const float* __restrict__ a_scale, const int* __restrict__ a_expert, const int* __restrict__ n_slots) {
+    __shared__ __align__(16) float As[BK][BM + 4];
+    __shared__ __align__(16) float Bs[BK][BN + 4];
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m_end = n_slots ? min(M, *n_slots) : M;
+    if (m0 >= m_end) return;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const __nv_bfloat16* Wb = W + (a_expert ? (size_t)a_expert[m0] * (size_t)w_expert_stride : 0);
+
+    // this thread's load coordinates: row (tid / 4) of the tile, 4 consecutive k
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    int src = -1;
+    float sc = 1.f;
+    if (m0 + lr < m_end) {
+        src = a_row ? a_row[m0 + lr] : m0 + lr;
+        if (a_scale && src >= 0) sc = a_scale[m0 + lr];
+    }
+    const float* arow = src >= 0 ? A + (size_t)src * lda : nullptr;
+    const __nv_bfloat16* wrow = (n0 + lr < N) ? Wb + (size_t)(n0 + lr) * K : nullptr;
+    const bool a_vec = (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    const bool w_vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(Wb) & 7) == 0);
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f};
+        const int k = k0 + lk;
+        if (arow) {
+            if (a_vec && k + 3 < K) {
+                const float4 v = *reinterpret_cast<const float4*>(arow + k);
+                a4[0] = v.x; a4[1] = v.y; a4[2] = v.z; a4[3] = v.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k + i < K) a4[i] = arow[k + i];
+            }
+        }
+        if (wrow) {
+            if (w_vec && k + 3 < K) {
+                const uint2 v = *reinterpret_cast<const uint2*>(wrow + k);
+                const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+                const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+                b4[0] = __low2float(p0); b4[1] = __high2float(p0); b4[2] = __low2float(p1); b4[3] = __high2float(p1);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k + i < K) b4[i] = bf(wrow[k + i]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            As[lk + i][lr] = a4[i] * sc;
+            Bs[lk + i][lr] = b4[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+            const float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int a = m0 + ty * 4 + i;
+        if (a >= m_end) continue;
+        if (a_row && a_row[a] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) Y[(size_t)a * ldy + n] = acc[i][j];
+        }
+    }
+}
+
+// one warp per output element (a, n); for a few rows (decoding): the weights stream once per row, 16 bytes per lane
+__global__ void __launch_bounds__(256)
+linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
+                   float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
+                   const float* __restrict__ a_scale, const int* __restrict__ a_expert, const int* __restrict__ n_slots) {
+    const int a = blockIdx.y;
+    const int m_end = n_slots ? min(M, *n_slots) : M;
+    if (a >= m_end) return;
+    const int src = a_row ? a_row[a] : a;
+    if (src < 0) return;
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const float sc = a_scale ? a_scale[a] : 1.f;
+    const float* arow = A + (size_t)src * lda;
+    const __nv_bfloat16* wrow = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
+    float acc = 0.f;
+    const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(arow) & 15) == 0);
+    if (vec) {
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k);
+            const float4 x0 = *reinterpret_cast<const float4*>(arow + k);
+            const float4 x1 = *reinterpret_cast<const float4*>(arow + k + 4);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            acc = fmaf(x0.x * sc, __low2float(p[0]), acc);
+            acc = fmaf(x0.y * sc, __high2float(p[0]), acc);
+            acc = fmaf(x0.z * sc, __low2float(p[1]), acc);
+            acc = fmaf(x0.w * sc, __high2float(p[1]), acc);
+            acc = fmaf(x1.x * sc, __low2float(p[2]), acc);
+            acc = fmaf(x1.y * sc, __high2float(p[2]), acc);
+            acc = fmaf(x1.z * sc, __low2float(p[3]), acc);
+            acc = fmaf(x1.w * sc, __high2float(p[3]), acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(arow[k] * sc, bf(wrow[k]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) Y[(size_t)a * ldy + n] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// qk rows are [q (nq) | k (nk)].  q <- q / rms(q) * qw in place; the raw k goes to the value pages, k / rms(k) * kw to the
+// key pages.  Pages: [page][kv head][page_size][dim] per layer; the sequence's page j / page_size is table[slot][..].
+__global__ void qk_norm_cache_kernel(float* __restrict__ qk, int nq, int nk, const float* __restrict__ qw,
+                                     const float* __restrict__ kw, float eps, float* __restrict__ kcache,
+                                     float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
+                                     int kv_heads, int dim, const int* __restrict__ row_slot,
+                                     const int* __restrict__ row_pos) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float* q = qk + (size_t)r * (nq + nk);
+    float* k = q + nq;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) sq = fmaf(q[c], q[c], sq);
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) sk = fmaf(k[c], k[c], sk);
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    const float rq = 1.0f / sqrtf(sq / (float)nq + eps), rk = 1.0f / sqrtf(sk / (float)nk + eps);
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) q[c] = q[c] * rq * qw[c];
+    const int pos = row_pos[r];
+    const int page = table[(size_t)row_slot[r] * max_pages + pos / page_size], off = pos % page_size;
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+        const int g = c / dim, d = c - g * dim;
+        const size_t at = (((size_t)page * kv_heads + g) * page_size + off) * dim + d;
+        const float raw = k[c];
+        vcache[at] = raw;
+        kcache[at] = raw * rk * kw[c];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One CTA per (row, query head).  Query position i sees key j <= i when i - j < window or j < keep_first (window <= 0:
+// every j <= i).  score = cap * tanh(q.k * scale * temp_h / cap) - slope_h * (i - j)  (cap <= 0: no cap).  The softmax
+// denominator also holds exp(sink_h) when a sink is given (no key, no value): the running maximum starts at the sink.
+constexpr int kAttnThreads = 128;
+constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnMaxDimPerLane = 8;                         // head dim <= 256
+
+__global__ void __launch_bounds__(kAttnThreads)
+sink_attention_kernel(const float* __restrict__ qk, int q_stride, const float* __restrict__ kcache,
+                      const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
+                      int heads, int kv_heads, int dim, float scale, float cap, const float* __restrict__ temp,
+                      const float* __restrict__ slopes, const float* __restrict__ sink, int window, int keep_first,
+                      const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out) {
+    extern __shared__ __align__(16) float sm[];
+    float* qs = sm;                                           // [dim]
+    float* ps = qs + ((dim + 3) & ~3);                        // [kAttnThreads]
+    float* acc_s = ps + kAttnThreads;                         // [kAttnWarps][dim]
+    __shared__ float red[32];
+    const int r = blockIdx.x, h = blockIdx.y;
+    const int g = h / (heads / kv_heads);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int i = row_pos[r];
+    const int* pages = table + (size_t)row_slot[r] * max_pages;
+    for (int c = tid; c < dim; c += kAttnThreads) qs[c] = qk[(size_t)r * q_stride + (size_t)h * dim + c];
+    const float mult = scale * (temp ? temp[h] : 1.f);
+    const float slope = slopes ? slopes[h] : 0.f;
+    const int lo = window > 0 ? max(0, i - window + 1) : 0;
+    const int n_keep = window > 0 ? min(keep_first, lo) : 0;
+    const int n_keys = n_keep + (i - lo + 1);
+    const bool vec = (dim % 4) == 0;
+
+    float m_run = sink ? sink[h] : -CUDART_INF_F;
+    float l_part = 0.f;                                       // this thread's share of the denominator
+    float acc[kAttnMaxDimPerLane];
+#pragma unroll
+    for (int u = 0; u < kAttnMaxDimPerLane; ++u) acc[u] = 0.f;
+    __syncthreads();
+
+    for (int t0 = 0; t0 < n_keys; t0 += kAttnThreads) {
+        const int kk = t0 + tid;
+        float s = -CUDART_INF_F;
+        if (kk < n_keys) {
+            const int j = kk < n_keep ? kk : lo + (kk - n_keep);
+            const float* kp = kcache + (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim;
+            float d = 0.f;
+            if (vec) {
+                for (int c = 0; c < dim; c += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kp + c);
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + c);
+                    d = fmaf(qv.x, kv.x, d); d = fmaf(qv.y, kv.y, d); d = fmaf(qv.z, kv.z, d); d = fmaf(qv.w, kv.w, d);
+                }
+            } else {
+                for (int c = 0; c < dim; ++c) d = fmaf(qs[c], kp[c], d);
+            }
+            s = d * mult;
+            if (cap > 0.f) s = cap * tanhf(s / cap);
+            s -= slope * (float)(i - j);
+        }
+        const float m_new = fmaxf(m_run, block_max(s, red));
+        const float corr = (m_run == -CUDART_INF_F) ? 0.f : expf(m_run - m_new);
+        const float p = (kk < n_keys) ? expf(s - m_new) : 0.f;
+        l_part = l_part * corr + p;
+#pragma unroll
+        for (int u = 0; u < kAttnMaxDimPerLane; ++u) acc[u] *= corr;
+        m_run = m_new;
+        __syncthreads();                                      // the previous tile's ps is consumed
+        ps[tid] = p;
+        __syncthreads();
+        const int n_tile = min(kAttnThreads, n_keys - t0);
+        for (int e = warp; e < n_tile; e += kAttnWarps) {
+            const int k2 = t0 + e;
+            const int j = k2 < n_keep ? k2 : lo + (k2 - n_keep);
+            const float* vp = vcache + (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim;
+            const float pe = ps[e];
+#pragma unroll
+            for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
+                const int c = lane + 32 * u;
+                if (c < dim) acc[u] = fmaf(pe, vp[c], acc[u]);
+            }
+        }
+    }
+    float l = block_sum(l_part, red);
+    if (sink) l += expf(sink[h] - m_run);                     // the sink's own term (exp(0) while it is the maximum)
+#pragma unroll
+    for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
+        const int c = lane + 32 * u;
+        if (c < dim) acc_s[warp * dim + c] = acc[u];
+    }
+    __syncthreads();
+    for (int c = tid; c < dim; c += kAttnThreads) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) o += acc_s[w * dim + c];
+        out[((size_t)r * heads + h) * dim + c] = o / l;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// one warp per row: scores s = sigmoid(z); the `top` largest (ties: the lower index) in descending order
+__global__ void router_topk_kernel(const float* __restrict__ z, int E, int top, int M, int* __restrict__ sel_e,
+                                   float* __restrict__ sel_w) {
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= M) return;
+    const float* zr = z + (size_t)r * E;
+    for (int t = 0; t < top; ++t) {
+        float best = -CUDART_INF_F;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            bool taken = false;
+            for (int u = 0; u < t; ++u) taken |= (sel_e[(size_t)r * top + u] == e);
+            const float v = zr[e];
+            if (!taken && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            sel_e[(size_t)r * top + t] = bi;
+            sel_w[(size_t)r * top + t] = 1.0f / (1.0f + expf(-best));
+        }
+        __syncwarp();
+    }
+}
+
+// one CTA: counts per expert, group starts padded to `pad` slots, then a_row / a_scale / a_expert per slot and the slot
+// of every assignment.  The order inside a group does not matter: every slot's row is computed on its own.
+__global__ void moe_group_kernel(const int* __restrict__ sel_e, const float* __restrict__ sel_w, int n_assign, int top,
+                                 int E, int pad, int* __restrict__ a_row, float* __restrict__ a_scale,
+                                 int* __restrict__ a_expert, int* __restrict__ slot_of, int* __restrict__ n_slots,
+                                 int max_slots) {
+    extern __shared__ int sh[];
+    int* count = sh;            // [E]
+    int* start = sh + E;        // [E]
+    int* cursor = sh + 2 * E;   // [E]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) atomicAdd(&count[sel_e[a]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + pad - 1) / pad * pad; }
+        *n_slots = at;
+    }
+    __syncthreads();
+    const int total = min(*n_slots, max_slots);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int end = (e + 1 < E) ? start[e + 1] : total;
+        for (int s = start[e]; s < end; ++s) { a_row[s] = -1; a_scale[s] = 0.f; a_expert[s] = e; }
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
+        const int e = sel_e[a];
+        const int s = start[e] + atomicAdd(&cursor[e], 1);
+        a_row[s] = a / top;
+        a_scale[s] = sel_w[a];
+        slot_of[a] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict__ mid, int F, const int* __restrict__ a_row,
+                                const int* __restrict__ n_slots, int M) {
+    const int a = blockIdx.x;
+    if (n_slots && a >= min(M, *n_slots)) return;
+    if (a_row && a_row[a] < 0) return;
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+        const float g = gu[(size_t)a * 2 * F + c], u = gu[(size_t)a * 2 * F + F + c];
+        mid[(size_t)a * F + c] = (g / (1.0f + expf(-g))) * u;
+    }
+}
+
+// x[r] += DynamicTanh(y[r] + sum_t parts[slot_of[r * top + t]])   (y or parts may be absent)
+__global__ void residual_dyt_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ parts,
+                                    const int* __restrict__ slot_of, int top, const float* __restrict__ nw,
+                                    const float* __restrict__ nb, float alpha, int D) {
+    const int r = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
+        float v = y ? y[(size_t)r * D + c] : 0.f;
+        if (parts)
+            for (int t = 0; t < top; ++t) v += parts[(size_t)slot_of[(size_t)r * top + t] * D + c];
+        if (nw) x[(size_t)r * D + c] += dyt(v, alpha, nw[c], nb[c]);
+        else x[(size_t)r * D + c] = v;                            // no norm given: the plain sum
+    }
+}
+
+__global__ void dyt_gather_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ nw,
+                                  const float* __restrict__ nb, float alpha, float* __restrict__ out, int D) {
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    for (int c = threadIdx.x; c < D; c += blockDim.x)
+        out[(size_t)blockIdx.x * D + c] = dyt(x[(size_t)r * D + c], alpha, nw[c], nb[c]);
+}
+
+// greedy sampling: index of the largest logit of every row (ties: the lowest index)
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    float best = -CUDART_INF_F;
+    int at = 0x7fffffff;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        const float v = row[c];
+        if (v > best || (v == best && c < at)) { best = v; at = c; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > best || (ov == best && oi < at)) { best = ov; at = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = at; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (bv[w] > best || (bv[w] == best && bi[w] < at)) { best = bv[w]; at = bi[w]; }
+        out[blockIdx.x] = at;
+    }
+}
+
+// ---- launchers --------------------------------------------------------------------------------------------------------
+cudaError_t launch_embed(const void* table, const int* ids, float* out, int M, int V, int D, cudaStream_t st) {
+    embed_rows_bf16_kernel<<<M, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(table), ids, out, V, D);
+    return cudaGetLastError();
+}
+
+static inline int col_blocks(int D) { return D > 1024 ? (D + 1023) / 1024 : 1; }
+
+cudaError_t launch_dyt_tapmix(const float* x, const NormW& n, const float* cw, int taps, const float* tail, const RowMeta& rm,
+                              float* out, int M, int D, cudaStream_t st) {
+    dyt_tapmix_kernel<<<dim3(M, col_blocks(D)), 256, 0, st>>>(x, n.w, n.b, n.alpha, cw, taps, tail, rm.slot, rm.pos, rm.start,
+                                                              out, D);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tapmix_tail(const float* x, const NormW& n, int taps, float* tail, const SeqMeta& sm, int n_seq, int D,
+                               cudaStream_t st) {
+    if (taps <= 1) return cudaSuccess;
+    tapmix_tail_kernel<<<dim3(n_seq, col_blocks(D)), 256, 0, st>>>(x, n.w, n.b, n.alpha, taps, tail, sm.slot, sm.row0, sm.count, D);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_linear(const float* A, int lda, const void* W, long long w_expert_stride, float* Y, int ldy, int M, int N,
+                          int K, const GroupMap* gm, cudaStream_t st) {
+    const int* a_row = gm ? gm->a_row : nullptr;
+    const float* a_scale = gm ? gm->a_scale : nullptr;
+    const int* a_expert = gm ? gm->a_expert : nullptr;
+    const int* n_slots = gm ? gm->n_slots : nullptr;
+    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
+    if (M <= kRowsKernelMax)
+        linear_rows_kernel<<<dim3((N + 7) / 8, M), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N, K, a_row, a_scale,
+                                                                 a_expert, n_slots);
+    else
+        linear_tile_kernel<<<dim3((N + BN - 1) / BN, (M + BM - 1) / BM), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N,
+                                                                                      K, a_row, a_scale, a_expert, n_slots);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,
+                                 float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
+                                 cudaStream_t st) {
+    qk_norm_cache_kernel<<<M, 256, 0, st>>>(qk, nq, nk, qw, kw, eps, kcache, vcache, pm.table, pm.max_pages, pm.page_size,
+                                            kv_heads, dim, rm.slot, rm.pos);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
+                                  const AttnShape& a, const RowMeta& rm, float* out, int M, cudaStream_t st) {
+    if (a.dim > 32 * kAttnMaxDimPerLane || a.heads % a.kv_heads) return cudaErrorNotSupported;
+    const size_t smem = (size_t)(((a.dim + 3) & ~3) + kAttnThreads + kAttnWarps * a.dim) * sizeof(float);
+    sink_attention_kernel<<<dim3(M, a.heads), kAttnThreads, smem, st>>>(
+        qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
+        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st) {
+    router_topk_kernel<<<(M + 3) / 4, 128, 0, st>>>(z, E, top, M, sel_e, sel_w);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign, int top, int E, int pad, const GroupMap& gm,
+                             int* slot_of, int max_slots, cudaStream_t st) {
+    moe_group_kernel<<<1, 256, 3 * E * sizeof(int), st>>>(sel_e, sel_w, n_assign, top, E, pad, gm.a_row, gm.a_scale, gm.a_expert,
+                                                          slot_of, gm.n_slots, max_slots);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(const float* gu, float* mid, int M, int F, const GroupMap* gm, cudaStream_t st) {
+    silu_mul_kernel<<<M, 256, 0, st>>>(gu, mid, F, gm ? gm->a_row : nullptr, gm ? gm->n_slots : nullptr, M);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_residual_dyt(float* x, const float* y, const float* parts, const int* slot_of, int top, const NormW& n, int M,
+                                int D, cudaStream_t st) {
+    residual_dyt_kernel<<<dim3(M, col_blocks(D)), 256, 0, st>>>(x, y, parts, slot_of, top, n.w, n.b, n.alpha, D);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, int M, int D, cudaStream_t st) {
+    dyt_gather_kernel<<<M, 256, 0, st>>>(x, rows, n.w, n.b, n.alpha, out, D);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_rows(const float* logits, int M, int V, int* out, cudaStream_t st) {
+    argmax_rows_kernel<<<M, 256, 0, st>>>(logits, V, out);
+    return cudaGetLastError();
+}
+
+}  // namespace lm

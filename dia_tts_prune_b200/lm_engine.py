@@ -1,0 +1,181 @@
+"""Python face of ``liblm_b200.so``: the step function of the decoder-only language-model path.
+
+``LMEngine.step`` takes the rows the scheduler picked - for each scheduled sequence its next tokens, a prompt portion
+or one decoded token alike - lays them out as one flat batch, and runs them through the kernels in portions of at most
+``max_rows`` rows.  All arithmetic is in ``csrc/``; there is no eager / CPU fallback here.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lm_lib
+from .lm_layers import DynamicTanh, MixLayer
+from .lm_state import PagedState, Sequence
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def launch_count() -> int:
+    return int(_lm_lib.load().lm_b200_launch_count())
+
+
+class LMEngine:
+    def __init__(self, layers: list[MixLayer], embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh, *,
+                 width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024):
+        if not torch.cuda.is_available():
+            raise RuntimeError("the language-model path needs a CUDA device (sm_100a); there is no CPU fallback")
+        self.lib = _lm_lib.load()
+        self.device = state.device
+        if self.device.type != "cuda":
+            raise RuntimeError("the sequence state must live on a CUDA device")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.layers, self.state = layers, state
+        self.embed = embed.detach().to(device=self.device, dtype=torch.bfloat16).contiguous()
+        self.head = head.detach().to(device=self.device, dtype=torch.bfloat16).contiguous()
+        self.final_norm = final_norm
+        self.width, self.vocab, self.max_rows = int(width), int(vocab), int(max_rows)
+        m = _lm_lib.Model()
+        m.n_layer, m.width, m.vocab, m.taps = len(layers), self.width, self.vocab, int(taps)
+        m.page_size, m.max_pages, m.n_slots, m.max_rows = state.page_size, state.max_pages, state.n_slots, self.max_rows
+        m.eps = float(eps)
+        m.embed, m.head = self.embed.data_ptr(), self.head.data_ptr()
+        final_norm.fill(m.final_norm)
+        m.page_table = state.page_table.data_ptr()
+        recs = (_lm_lib.Layer * len(layers))()
+        for i, layer in enumerate(layers):
+            layer.fill(recs[i], state.k_pages[i], state.v_pages[i], state.tails[i][0], state.tails[i][1])
+        self._h = C.c_void_p()
+        _lm_lib.check(self.lib.lm_b200_engine_create(C.byref(m), recs, self.device.index, C.byref(self._h)), "engine_create")
+        self.workspace_bytes = int(self.lib.lm_b200_engine_workspace_bytes(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self.lib.lm_b200_engine_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- one launch sequence over <= max_rows rows -----------------------------------------------------------
+    def _pack(self, parts: list[tuple[Sequence, list[int], int, list[int]]]) -> tuple[torch.Tensor, int, int, int]:
+        """parts: (sequence, tokens, position of the first token, wanted indexes into tokens) -> the step buffer."""
+        tok, slot, pos, start, s_slot, s_row0, s_count, want = [], [], [], [], [], [], [], []
+        for seq, tokens, p0, w in parts:
+            r0 = len(tok)
+            n = len(tokens)
+            tok += tokens
+            slot += [seq.slot] * n
+            pos += range(p0, p0 + n)
+            start += [p0] * n
+            s_slot.append(seq.slot)
+            s_row0.append(r0)
+            s_count.append(n)
+            want += [r0 + k for k in w]
+        buf = torch.tensor(tok + slot + pos + start + s_slot + s_row0 + s_count + want, dtype=torch.int32)
+        return buf.pin_memory().to(self.device, non_blocking=True), len(tok), len(parts), len(want)
+
+    def _forward(self, parts, logits_out: torch.Tensor | None, layers_out: torch.Tensor | None = None) -> None:
+        buf, M, S, W = self._pack(parts)
+        self.state.sync_table()
+        _lm_lib.check(self.lib.lm_b200_forward(
+            self._h, buf.data_ptr(), M, S, W, logits_out.data_ptr() if W else None,
+            layers_out.data_ptr() if layers_out is not None else None, _stream(self.device)), "forward")
+        self._keep = buf                                        # stays alive until the next call is queued behind it
+
+    def step(self, entries: list[tuple[Sequence, list[int], list[int]]], keep_layers: bool = False):
+        """entries: (sequence, its next tokens, indexes among them whose logits are wanted).  Appends the tokens to the
+        sequences' state and returns float32 logits ``[wanted, vocab]`` in the order of the entries (and, with
+        ``keep_layers``, the residual stream after every layer for all rows)."""
+        n_want = sum(len(w) for _, _, w in entries)
+        total = sum(len(t) for _, t, _ in entries)
+        logits = torch.empty((n_want, self.vocab), dtype=torch.float32, device=self.device)
+        streams = torch.empty((len(self.layers), total, self.width), dtype=torch.float32, device=self.device) if keep_layers else None
+        if keep_layers and total > self.max_rows:
+            raise ValueError("keep_layers needs the whole step in one portion")
+        for seq, tokens, _ in entries:
+            self.state.reserve(seq, len(tokens))
+        parts, rows, done = [], 0, 0
+
+        def flush():
+            nonlocal parts, rows, done
+            if not parts:
+                return
+            w = sum(len(p[3]) for p in parts)
+            self._forward(parts, logits[done:done + w] if w else None, streams)
+            done += w
+            parts, rows = [], 0
+
+        order, base = [], 0                                     # logits are produced in row order; `want` may not be
+        for _, _, want in entries:
+            order += [base + k for k in sorted(range(len(want)), key=lambda i: want[i])]
+            base += len(want)
+        for seq, tokens, want in entries:
+            at, want = 0, sorted(want)
+            if want and (want[0] < 0 or want[-1] >= len(tokens)):
+                raise ValueError("a wanted place lies outside the entry's tokens")
+            while at < len(tokens):
+                n = min(len(tokens) - at, self.max_rows - rows)
+                parts.append((seq, list(tokens[at:at + n]), seq.length, [k - at for k in want if at <= k < at + n]))
+                self.state.advance(seq, n)
+                rows += n
+                at += n
+                if rows == self.max_rows:
+                    flush()
+        flush()
+        if order != list(range(n_want)):
+            inverse = [0] * n_want
+            for produced, asked in enumerate(order):
+                inverse[asked] = produced
+            logits = logits[torch.tensor(inverse, device=self.device)]
+        return (logits, streams) if keep_layers else logits
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        if logits.shape[0]:
+            _lm_lib.check(self.lib.lm_b200_argmax_rows(logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(),
+                                                       _stream(self.device)), "argmax_rows")
+        return out
+
+    # ---- operator boundaries (one mechanism at a time; used by the parity tests) ----------------------------------
+    def op_norm_tapmix(self, layer: int, sub: int, x: torch.Tensor, parts) -> torch.Tensor:
+        buf, M, S, _ = self._pack([(s, [0] * n, p0, []) for s, n, p0 in parts])
+        x = x.to(device=self.device, dtype=torch.float32).contiguous()
+        out = torch.empty_like(x)
+        _lm_lib.check(self.lib.lm_b200_op_norm_tapmix(self._h, layer, sub, x.data_ptr(), buf.data_ptr(), M, S, out.data_ptr(),
+                                                      _stream(self.device)), "op_norm_tapmix")
+        return out
+
+    def op_mixer(self, layer: int, h: torch.Tensor, parts) -> torch.Tensor:
+        buf, M, S, _ = self._pack([(s, [0] * n, p0, []) for s, n, p0 in parts])
+        self.state.sync_table()
+        h = h.to(device=self.device, dtype=torch.float32).contiguous()
+        y = torch.empty((M, self.width), dtype=torch.float32, device=self.device)
+        _lm_lib.check(self.lib.lm_b200_op_mixer(self._h, layer, h.data_ptr(), buf.data_ptr(), M, S, y.data_ptr(),
+                                                _stream(self.device)), "op_mixer")
+        return y
+
+    def op_ff(self, layer: int, h: torch.Tensor) -> torch.Tensor:
+        h = h.to(device=self.device, dtype=torch.float32).contiguous()
+        y = torch.empty_like(h)
+        _lm_lib.check(self.lib.lm_b200_op_ff(self._h, layer, h.data_ptr(), h.shape[0], y.data_ptr(), _stream(self.device)), "op_ff")
+        return y
+
+
+def linear(a: torch.Tensor, w_bf16: torch.Tensor) -> torch.Tensor:
+    """``a [M, K] float32 @ w [N, K]^T bfloat16`` on the path's own linear kernels."""
+    lib = _lm_lib.load()
+    a = a.to(torch.float32).contiguous()
+    w = w_bf16.to(torch.bfloat16).contiguous()
+    y = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float32, device=a.device)
+    _lm_lib.check(lib.lm_b200_op_linear(a.data_ptr(), w.data_ptr(), y.data_ptr(), a.shape[0], w.shape[0], a.shape[1],
+                                        _stream(a.device)), "op_linear")
+    return y

@@ -1,0 +1,214 @@
+"""``CausalLM``: the decoder-only language models behind the framework's serving interface.
+
+``CausalLM.from_pretrained(folder)`` reads ``config.json`` + ``model.safetensors``, builds the layer stack out of the
+mechanisms of ``lm_layers.py`` and binds it to an :class:`~.lm_engine.LMEngine` with a paged sequence state.  Requests
+then go through one scheduler (:class:`Scheduler`): it admits waiting requests while slots and pages last, feeds prompt
+portions and decode rows of all running requests to the SAME step function as one flat batch, samples, and gives the
+state of finished requests back.  ``generate`` (token ids in, token ids out - these models ship no tokenizer) and the
+teacher-forced ``run_step`` of the trace replayer both sit on it.
+"""
+
+from __future__ import annotations
+
+import json
+from collections import deque
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import torch
+
+from .checkpoint import load_safetensors
+from .lm_config import PubopelConfig
+from .lm_engine import LMEngine
+from .lm_layers import DynamicTanh, MixLayer, RoutedExperts, SinkAttention, TapMix
+from .lm_state import OutOfPages, PagedState, Sequence
+
+
+def distance_slopes(heads: int) -> torch.Tensor:
+    """Per-head slope of the linear distance bias of the Pubopel design: 2^(-8 (h + 1) / heads)."""
+    return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=torch.float64).to(torch.float32)
+
+
+def build_pubopel_layers(cfg: PubopelConfig, w: dict[str, torch.Tensor], device) -> tuple[list[MixLayer], DynamicTanh]:
+    """The layer stack of a Pubopel checkpoint (tensor names ``l<i>.norm1``, ``l<i>.mix.q``, ``l<i>.mlp.e<j>.gate`` ...)."""
+
+    def norm(name: str) -> DynamicTanh:
+        return DynamicTanh(w[name], w[name + ".b"], float(w[name + ".alpha"].float().item()), device)
+
+    layers = []
+    for i, lc in enumerate(cfg.layers):
+        p, m = f"l{i}.", lc.mixer
+        attn = SinkAttention(w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.q.norm"], w[p + "mix.k.norm"], w[p + "mix.o"],
+                             heads=m.heads, kv_heads=m.kv_heads, dim=m.dim, scale=m.scale, temp=w[p + "mix.temp"],
+                             slopes=distance_slopes(m.heads), sink=w[p + "mix.sink"], softcap=m.softcap,
+                             window=m.mask.size if m.mask else None, keep_first=m.mask.keep_first if m.mask else 0,
+                             device=device)
+        ff = n2 = n2b = t2 = None
+        if lc.mlp is not None:
+            E = lc.mlp.router.experts
+            shared = None
+            if lc.mlp.shared is not None:
+                shared = (w[p + "mlp.shared.gate"], w[p + "mlp.shared.up"], w[p + "mlp.shared.down"])
+            ff = RoutedExperts(w[p + "mlp.router"], [w[p + f"mlp.e{e}.gate"] for e in range(E)],
+                               [w[p + f"mlp.e{e}.up"] for e in range(E)], [w[p + f"mlp.e{e}.down"] for e in range(E)],
+                               top=lc.mlp.router.top, shared=shared, device=device)
+            n2, n2b, t2 = norm(p + "norm2"), norm(p + "norm2b"), TapMix(w[p + "canon2"], device)
+        layers.append(MixLayer(attn, norm(p + "norm1"), norm(p + "norm1b"), TapMix(w[p + "canon1"], device), ff, n2, n2b, t2))
+    return layers, norm("final.norm")
+
+
+@dataclass
+class Request:
+    name: str
+    prompt: list[int]
+    max_new_tokens: int
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int | None = None
+    eos: int | None = None
+    output: list[int] = field(default_factory=list)
+    fed: int = 0                      # prompt tokens already in the state
+    seq: Sequence | None = None
+    done: bool = False
+
+
+class Scheduler:
+    """Continuous batching over one engine: every iteration is one ``LMEngine.step`` over the decode rows of the running
+    requests and as many prompt rows (whole prompts or portions) as ``max_step_tokens`` leaves room for."""
+
+    def __init__(self, model: "CausalLM", max_step_tokens: int | None = None):
+        self.model = model
+        self.max_step_tokens = int(max_step_tokens or model.engine.max_rows)
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+
+    def add(self, req: Request) -> None:
+        if not req.prompt:
+            raise ValueError("a request needs at least one prompt token")
+        self.waiting.append(req)
+
+    def _admit(self) -> None:
+        st = self.model.state
+        while self.waiting and st.free_slots > 0:
+            req = self.waiting[0]
+            # room for the whole prompt and the tokens it may generate, so a running request never starves
+            if st.pages_needed(None, len(req.prompt) + req.max_new_tokens) > st.free_pages - self._promised():
+                break
+            self.waiting.popleft()
+            req.seq = st.open(req.name)
+            self.running.append(req)
+
+    def _promised(self) -> int:
+        st = self.model.state
+        return sum(st.pages_needed(r.seq, len(r.prompt) + r.max_new_tokens - r.seq.length) for r in self.running)
+
+    def iterate(self) -> list[Request]:
+        """One engine step; returns the requests that finished in it."""
+        self._admit()
+        if not self.running:
+            if self.waiting:
+                raise OutOfPages("the first waiting request does not fit the sequence state")
+            return []
+        budget, entries, sampled = self.max_step_tokens, [], []
+        for req in self.running:                               # decode rows first: they are one token each
+            if req.fed == len(req.prompt) and budget > 0:
+                entries.append((req.seq, [req.output[-1]], [0]))
+                sampled.append(req)
+                budget -= 1
+        for req in self.running:
+            if req.fed < len(req.prompt) and budget > 0:
+                n = min(budget, len(req.prompt) - req.fed)
+                last = req.fed + n == len(req.prompt)
+                entries.append((req.seq, req.prompt[req.fed:req.fed + n], [n - 1] if last else []))
+                req.fed += n
+                budget -= n
+                if last:
+                    sampled.append(req)
+        logits = self.model.engine.step(entries)
+        tokens = self.model.sample(logits, sampled).tolist() if sampled else []
+        finished = []
+        for req, tok in zip(sampled, tokens):
+            req.output.append(int(tok))
+            if len(req.output) >= req.max_new_tokens or (req.eos is not None and tok == req.eos):
+                req.done = True
+                finished.append(req)
+        for req in finished:
+            self.running.remove(req)
+            self.model.state.close(req.name)
+        return finished
+
+    def run(self) -> None:
+        while self.waiting or self.running:
+            self.iterate()
+
+
+class CausalLM:
+    def __init__(self, cfg: PubopelConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
+                 max_tokens: int = 4096, max_sequences: int = 8, page_size: int = 16, max_rows: int = 1024,
+                 max_sequence_tokens: int | None = None):
+        if dtype not in ("bfloat16", "float32"):
+            raise ValueError("dtype must be 'bfloat16' or 'float32'")
+        if not torch.cuda.is_available():
+            raise RuntimeError("the language-model path needs a CUDA device (sm_100a); there is no CPU fallback")
+        cfg.check()
+        self.config, self.dtype = cfg, dtype
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.layers, final_norm = build_pubopel_layers(cfg, weights, self.device)
+        self.state = PagedState([(lc.mixer.kv_heads, lc.mixer.dim) for lc in cfg.layers], cfg.width, cfg.canon.taps,
+                                max_tokens, self.device, page_size=page_size, max_sequences=max_sequences,
+                                max_sequence_tokens=max_sequence_tokens)
+        # Both dtypes keep activations, norms, scores and pages in float32 and the matrices in bfloat16 (as stored), the
+        # precision split of this framework's other model; float32 is therefore exact 32-bit arithmetic on the stored weights.
+        self.engine = LMEngine(self.layers, weights["embed"], weights["head"], final_norm, width=cfg.width, vocab=cfg.vocab,
+                               taps=cfg.canon.taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows)
+        self._draws = 0
+
+    @classmethod
+    def from_pretrained(cls, folder: str | Path, dtype: str = "bfloat16", device=None, **kw) -> "CausalLM":
+        folder = Path(folder)
+        cfg = PubopelConfig.model_validate(json.loads((folder / "config.json").read_text(encoding="utf-8")))
+        return cls(cfg, load_safetensors(folder / "model.safetensors"), dtype=dtype, device=device, **kw)
+
+    # ---- teacher-forced stepping (trace replay, scoring) -------------------------------------------------------
+    def run_step(self, entries: list[dict], end: list[str] = (), keep_layers: bool = False):
+        """``entries``: ``{"id", "tokens", "want"}`` per request - its next tokens and the places among them whose logits
+        are wanted.  A new id opens a sequence; ids in ``end`` are closed after the step.  Returns float32 logits
+        ``[wanted, vocab]`` on the device."""
+        rows = []
+        for ent in entries:
+            seq = self.state.sequences.get(ent["id"]) or self.state.open(ent["id"])
+            rows.append((seq, [int(t) for t in ent["tokens"]], [int(k) for k in ent.get("want", [])]))
+        out = self.engine.step(rows, keep_layers=keep_layers)
+        for name in end:
+            if name in self.state.sequences:
+                self.state.close(name)
+        return out
+
+    # ---- sampling ------------------------------------------------------------------------------------------------
+    def sample(self, logits: torch.Tensor, reqs: list[Request]) -> torch.Tensor:
+        """Greedy rows through the argmax kernel; the others through the framework's sampling helper."""
+        out = self.engine.argmax(logits)
+        hot = [i for i, r in enumerate(reqs) if r.temperature > 0.0]
+        if hot:
+            from .model import _sample_next_token
+            for i in hot:
+                r = reqs[i]
+                out[i] = _sample_next_token(logits[i:i + 1], r.temperature, r.top_p, r.top_k)[0].to(torch.int32)
+        return out
+
+    # ---- generation ------------------------------------------------------------------------------------------------
+    @torch.inference_mode()
+    def generate(self, prompts: list[list[int]], max_new_tokens: int = 16, temperature: float = 0.0, top_p: float = 1.0,
+                 top_k: int | None = None, eos: int | None = None, seed: int | None = None,
+                 max_step_tokens: int | None = None) -> list[list[int]]:
+        """Continues every prompt (token ids) by up to ``max_new_tokens`` tokens; greedy when ``temperature`` is 0."""
+        if seed is not None:
+            torch.manual_seed(seed)
+        sched = Scheduler(self, max_step_tokens)
+        reqs = [Request(name=f"g{self._draws}_{i}", prompt=[int(t) for t in p], max_new_tokens=int(max_new_tokens),
+                        temperature=float(temperature), top_p=float(top_p), top_k=top_k, eos=eos) for i, p in enumerate(prompts)]
+        self._draws += 1
+        for r in reqs:
+            sched.add(r)
+        sched.run()
+        return [r.output for r in reqs]

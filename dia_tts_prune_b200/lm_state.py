@@ -1,0 +1,110 @@
+"""Sequence state of the language-model path: paged K/V storage, per-sequence slots and short-convolution tails.
+
+Same role as ``state.py`` has for Dia (``KVCache`` / ``DecoderInferenceState``), but for any number of concurrent
+sequences of unknown final length: a sequence owns a *slot* (a row of the page table and of every layer's tail
+buffers) and a list of fixed-size *pages* of the shared K/V pool, taken when its length crosses a page border and
+given back when it ends.  Slots and pages are recycled last-freed-first.  The kernels read the device copy of the
+page table; the bookkeeping is host-side and never reads a device tensor.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+class OutOfPages(RuntimeError):
+    """The pool cannot hold the tokens asked for (the scheduler keeps the request waiting instead)."""
+
+
+@dataclass
+class Sequence:
+    """One live request: its slot, how many tokens its state holds, and the pages that hold them."""
+    name: str
+    slot: int
+    length: int = 0
+    pages: list[int] = field(default_factory=list)
+
+
+class PagedState:
+    def __init__(self, layers: list[tuple[int, int]], width: int, taps: int, max_tokens: int, device: torch.device,
+                 page_size: int = 16, max_sequences: int = 8, max_sequence_tokens: int | None = None):
+        """``layers``: (kv_heads, dim) of every layer.  ``max_tokens``: the most tokens all live sequences hold at one
+        time; the pool gets that many tokens' worth of pages plus one partly filled page per slot."""
+        if page_size <= 0 or max_tokens <= 0 or max_sequences <= 0:
+            raise ValueError("page_size, max_tokens and max_sequences must be positive")
+        self.device = torch.device(device)
+        self.page_size, self.n_slots = int(page_size), int(max_sequences)
+        longest = int(max_sequence_tokens or max_tokens)
+        self.max_pages = -(-longest // self.page_size)
+        self.n_pages = -(-int(max_tokens) // self.page_size) + self.n_slots
+        self.taps = int(taps)
+        # K (normed keys) and V (raw keys) pages per layer: [page][kv head][page_size][dim], float32
+        self.k_pages = [torch.zeros((self.n_pages, g, self.page_size, d), dtype=torch.float32, device=self.device)
+                        for g, d in layers]
+        self.v_pages = [torch.zeros_like(k) for k in self.k_pages]
+        # the last taps - 1 normed inputs of both sublayers of every layer: [slot][taps - 1][width]
+        t1 = max(self.taps - 1, 1)
+        self.tails = [(torch.zeros((self.n_slots, t1, width), dtype=torch.float32, device=self.device),
+                       torch.zeros((self.n_slots, t1, width), dtype=torch.float32, device=self.device)) for _ in layers]
+        self._table_host = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32).pin_memory() \
+            if self.device.type == "cuda" else torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32)
+        self.page_table = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32, device=self.device)
+        self._dirty = False
+        self._free_pages = list(range(self.n_pages - 1, -1, -1))        # pop() takes page 0 first
+        self._free_slots = list(range(self.n_slots - 1, -1, -1))
+        self.sequences: dict[str, Sequence] = {}
+
+    # ---- bookkeeping -----------------------------------------------------------------------------------------
+    @property
+    def free_pages(self) -> int:
+        return len(self._free_pages)
+
+    @property
+    def free_slots(self) -> int:
+        return len(self._free_slots)
+
+    def pages_needed(self, seq: Sequence | None, new_tokens: int) -> int:
+        have = len(seq.pages) if seq is not None else 0
+        length = seq.length if seq is not None else 0
+        return max(0, -(-(length + new_tokens) // self.page_size) - have)
+
+    def open(self, name: str) -> Sequence:
+        if name in self.sequences:
+            raise ValueError(f"sequence {name!r} is already open")
+        if not self._free_slots:
+            raise OutOfPages("no free sequence slot")
+        seq = Sequence(name=name, slot=self._free_slots.pop())
+        self.sequences[name] = seq
+        return seq
+
+    def reserve(self, seq: Sequence, new_tokens: int) -> None:
+        """Make room for ``new_tokens`` more tokens of ``seq`` (takes pages; the length moves in :meth:`advance`)."""
+        need = self.pages_needed(seq, new_tokens)
+        if len(seq.pages) + need > self.max_pages:
+            raise OutOfPages(f"sequence {seq.name!r} would exceed {self.max_pages * self.page_size} tokens")
+        if need > len(self._free_pages):
+            raise OutOfPages(f"{need} pages needed, {len(self._free_pages)} free")
+        for _ in range(need):
+            p = self._free_pages.pop()
+            self._table_host[seq.slot, len(seq.pages)] = p
+            seq.pages.append(p)
+            self._dirty = True
+
+    def advance(self, seq: Sequence, new_tokens: int) -> None:
+        seq.length += int(new_tokens)
+
+    def close(self, name: str) -> None:
+        """Give a finished sequence's pages and slot back."""
+        seq = self.sequences.pop(name)
+        self._free_pages.extend(reversed(seq.pages))
+        self._free_slots.append(seq.slot)
+        seq.pages = []
+
+    def sync_table(self) -> torch.Tensor:
+        """The device page table, refreshed if pages were taken since the last call (stream-ordered copy)."""
+        if self._dirty:
+            self.page_table.copy_(self._table_host, non_blocking=True)
+            self._dirty = False
+        return self.page_table
