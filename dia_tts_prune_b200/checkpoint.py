@@ -48,7 +48,10 @@ def load_safetensors(path: str | Path) -> dict[str, torch.Tensor]:
         count = int(np.prod(shape)) if shape else 1
         if end - begin != count * size or end > data.numel():
             raise ValueError(f"{path}: tensor {name!r} has inconsistent offsets")
-        out[name] = data[begin:end].view(dtype).reshape(shape)
+        raw = data[begin:end]
+        if begin % size:                                        # a view needs the element's alignment
+            raw = raw.clone()
+        out[name] = raw.view(dtype).reshape(shape)
     return out
 
 

@@ -4,7 +4,9 @@
 // token, each row carrying (sequence slot, position, position of the first row its sequence has in this step).  Prompt
 // portions, single decoded tokens and mixed batches are the same launch sequence.  Every kernel here computes a row's
 // result from that row (and the sequence state it points at) alone, in an order of operations that does not depend on
-// which other rows are in the batch - so the value at a position is bit-identical however the prompt was cut.
+// which other rows are in the batch - so the value at a position does not depend on how the prompt was cut or batched.
+// (The only thing the row count selects is which of the two linear kernels runs; they sum in different orders, so a
+// position computed in a step of a few rows and in a long one agrees to rounding, and to the bit within either kind.)
 //
 // Precision: activations, the residual stream, norms, router, attention scores / weights and the K/V pages are fp32;
 // matrices are bf16 in memory and multiplied with fp32 accumulation.
@@ -14,7 +16,7 @@
 //                              identity added), previous inputs from the step itself or from the sequence's tail state
 //   tapmix_tail_kernel         keeps the last taps-1 normed inputs of every scheduled sequence
 //   linear_tile_kernel         Y = A . W^T, 64 x 64 x 16 tiles of fp32 FMAs, optional row gather / scale / per-tile expert
-//   linear_rows_kernel         the same contract for a handful of rows: one warp per output element
+//   linear_rows_kernel         the same interface for a handful of rows: one warp per output element
 //   qk_norm_cache_kernel       whole-projection RMS norm of q and k, raw k and normed k scattered into the paged cache
 //   sink_attention_kernel      softmax attention over the pages with per-head temperature, tanh cap, linear distance
 //                              bias, a window that keeps the first tokens, and a value-less sink term in the denominator

@@ -174,11 +174,19 @@ class CausalLM:
         """``entries``: ``{"id", "tokens", "want"}`` per request - its next tokens and the places among them whose logits
         are wanted.  A new id opens a sequence; ids in ``end`` are closed after the step.  Returns float32 logits
         ``[wanted, vocab]`` on the device."""
-        rows = []
-        for ent in entries:
-            seq = self.state.sequences.get(ent["id"]) or self.state.open(ent["id"])
-            rows.append((seq, [int(t) for t in ent["tokens"]], [int(k) for k in ent.get("want", [])]))
-        out = self.engine.step(rows, keep_layers=keep_layers)
+        rows, opened = [], []
+        try:
+            for ent in entries:
+                seq = self.state.sequences.get(ent["id"])
+                if seq is None:
+                    seq = self.state.open(ent["id"])
+                    opened.append(ent["id"])
+                rows.append((seq, [int(t) for t in ent["tokens"]], [int(k) for k in ent.get("want", [])]))
+            out = self.engine.step(rows, keep_layers=keep_layers)
+        except OutOfPages:
+            for name in opened:                                 # a request that does not fit leaves nothing behind
+                self.state.close(name)
+            raise
         for name in end:
             if name in self.state.sequences:
                 self.state.close(name)
