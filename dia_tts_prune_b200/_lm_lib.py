@@ -13,6 +13,7 @@ from . import build as _build
 
 MIXER_SINK_ATTENTION = 1
 FF_NONE, FF_ROUTED_EXPERTS = 0, 1
+PRECISION_FP32, PRECISION_BF16 = 0, 1
 E_OK, E_INVAL, E_CUDA, E_NOMEM, E_UNSUPPORTED = 0, -1, -2, -3, -5
 
 _vp, _i, _f = C.c_void_p, C.c_int32, C.c_float
@@ -33,7 +34,7 @@ class Layer(C.Structure):
 
 class Model(C.Structure):
     _fields_ = [("n_layer", _i), ("width", _i), ("vocab", _i), ("taps", _i), ("page_size", _i), ("max_pages", _i),
-                ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("reserved", _i), ("embed", _vp), ("head", _vp),
+                ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("precision", _i), ("embed", _vp), ("head", _vp),
                 ("final_norm", Norm), ("page_table", _vp)]
 
 
@@ -50,6 +51,7 @@ _SIGNATURES = {
     "lm_b200_op_mixer": (_ci, [_vp, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
     "lm_b200_op_ff": (_ci, [_vp, _ci, _vp, _ci, _vp, _vp]),
     "lm_b200_op_linear": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "lm_b200_op_linear_tc": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "lm_b200_argmax_rows": (_ci, [_vp, _ci, _ci, _vp, _vp]),
 }
 

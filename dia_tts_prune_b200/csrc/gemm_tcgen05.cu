@@ -19,6 +19,11 @@
 //             fp32 stores) while the MMAs of tile i + 1 fill the other accumulator
 // W is kept as a K-major bf16 copy [N][K] made once per weight (transpose_to_bf16_kernel), so that A and B use the
 // same canonical UMMA layout.  Every wait is bounded (a stuck pipeline traps instead of hanging the GPU).
+//
+// The same kernel serves callers whose activations are bf16 already (terms = 1: one MMA per k-step, the operand is read
+// as it is), row tiles that belong to different weight matrices (expert groups: the group of a tile's first row picks
+// the matrix, a device-side row count skips the unused tiles), a contraction length that is not a multiple of the
+// k-block (the TMA fills the tail of both operands with zeros) and a DynamicTanh in front of the residual add.
 #include <algorithm>
 
 #include <cuda.h>
@@ -26,6 +31,7 @@
 
 #include "common.cuh"
 #include "engine_internal.h"
+#include "gemm_tcgen05.h"
 
 namespace dia {
 
@@ -35,7 +41,7 @@ namespace {
 // by the operand traffic from L2 (BN = 128 moved 4.3 GB for M = 2048, N = 16384, K = 2048: 13 TB/s at 326 us), and a
 // 256-wide MMA (128-cycle floor) also hides the ~100 cycles one tcgen05.mma takes to issue.
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int kTerms = 3;
+constexpr int kTerms = 3;                                   // terms of an fp32 activation (the most a call may stack)
 constexpr int kASlots = 7, kBSlots = 3;                     // A-term ring / weight ring: > 2 k-blocks of operands in flight
 constexpr int kTileBytes = BM * BK * 2;                     // 16 KB: one [128 x 64] bf16 tile
 constexpr int kBTileBytes = BN * BK * 2;                    // 32 KB: the weight tile
@@ -140,7 +146,8 @@ __global__ void transpose_to_bf16_kernel(const void* __restrict__ w, int src_bf1
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        float* y, const float* residual, int M, int N, int K) {
+                        float* y, const float* residual, int M, int N, int K, int terms, const float* dyt_w,
+                        const float* dyt_b, float dyt_alpha, const int* row_group, int group_rows, const int* n_rows) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* a_ring = smem;
@@ -154,7 +161,8 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(t_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_kb = K / BK;
+    const int n_kb = (K + BK - 1) / BK;                    // a partial last k-block reads zeros beyond K in both operands
+    const int m_lim = n_rows ? min(M, *n_rows) : M;        // row tiles at or beyond it hold no rows: every role skips them
     // tile t = (column block t / tiles_m, row block t % tiles_m): the CTAs of a wave share a few weight blocks and all of A
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, n_tiles = tiles_m * tiles_n;
 
@@ -179,15 +187,17 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             unsigned ia = 0, ib = 0;                        // ring positions, running across the tiles
             for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
                 const int n0 = (t / tiles_m) * BN, m0 = (t % tiles_m) * BM;
+                if (m0 >= m_lim) continue;
+                const int b_row0 = n0 + (row_group ? row_group[m0] * group_rows : 0);   // the tile's weight matrix
                 for (int kb = 0; kb < n_kb; ++kb) {
                     {
                         const unsigned s = ib % kBSlots;
                         mbar_wait_bounded(&b_empty[s], ((ib / kBSlots) & 1u) ^ 1u);
                         mbar_arrive_expect_tx(&b_full[s], kBTileBytes);
-                        tma_load_2d(smem_u32(b_ring + s * kBTileBytes), &map_b, smem_u32(&b_full[s]), kb * BK, n0);
+                        tma_load_2d(smem_u32(b_ring + s * kBTileBytes), &map_b, smem_u32(&b_full[s]), kb * BK, b_row0);
                         ++ib;
                     }
-                    for (int tm = 0; tm < kTerms; ++tm) {   // rows of term tm start at tm * M in the stacked matrix
+                    for (int tm = 0; tm < terms; ++tm) {   // rows of term tm start at tm * M in the stacked matrix
                         const unsigned s = ia % kASlots;
                         mbar_wait_bounded(&a_empty[s], ((ia / kASlots) & 1u) ^ 1u);
                         mbar_arrive_expect_tx(&a_full[s], kTileBytes);
@@ -202,7 +212,8 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major, N = 256, M = 128
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         unsigned ia = 0, ib = 0, it = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+            if ((t % tiles_m) * BM >= m_lim) continue;
             const unsigned acc = it & 1u;
             mbar_wait_bounded(&t_empty[acc], ((it >> 1) & 1u) ^ 1u);      // the epilogue has drained this accumulator
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -211,8 +222,7 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 const unsigned sb = ib % kBSlots;
                 mbar_wait_bounded(&b_full[sb], (ib / kBSlots) & 1u);
                 const uint64_t bdesc = umma_desc(smem_u32(b_ring + sb * kBTileBytes));
-#pragma unroll
-                for (int tm = 0; tm < kTerms; ++tm) {
+                for (int tm = 0; tm < terms; ++tm) {
                     const unsigned sa = ia % kASlots;
                     mbar_wait_bounded(&a_full[sa], (ia / kASlots) & 1u);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -222,7 +232,7 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         for (int j = 0; j < BK / 16; ++j)       // advance 16 elements = 32 bytes = 2 descriptor units along K
                             umma_bf16(d, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | tm | j) != 0 ? 1u : 0u);
                         umma_commit(&a_empty[sa]);              // the slot is free once these MMAs have read it
-                        if (tm == kTerms - 1) umma_commit(&b_empty[sb]);
+                        if (tm == terms - 1) umma_commit(&b_empty[sb]);
                     }
                     __syncwarp();
                     ++ia;
@@ -231,13 +241,15 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             }
             if (elect_one_sync()) umma_commit(&t_full[acc]);    // the accumulator is complete
             __syncwarp();
+            ++it;
         }
     } else {
         // ===== epilogue: a warp may touch the 32 TMEM lanes of its quarter (warp id mod 4) =====
         const int q = warp & 3;
         unsigned it = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
             const int n0 = (t / tiles_m) * BN, m0 = (t % tiles_m) * BM;
+            if (m0 >= m_lim) continue;
             const unsigned acc = it & 1u;
             mbar_wait_bounded(&t_full[acc], (it >> 1) & 1u);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -268,6 +280,12 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         if (c0 + 4 * i + 4 <= N) {
                             float4 a = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
                                                    __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                            if (dyt_w) {                        // DynamicTanh of the product: tanh(alpha a) w + b per column
+                                const float4 w4 = *reinterpret_cast<const float4*>(dyt_w + c0 + 4 * i);
+                                const float4 b4 = *reinterpret_cast<const float4*>(dyt_b + c0 + 4 * i);
+                                a.x = fmaf(tanhf(dyt_alpha * a.x), w4.x, b4.x); a.y = fmaf(tanhf(dyt_alpha * a.y), w4.y, b4.y);
+                                a.z = fmaf(tanhf(dyt_alpha * a.z), w4.z, b4.z); a.w = fmaf(tanhf(dyt_alpha * a.w), w4.w, b4.w);
+                            }
                             if (res) {
                                 const float4 r4 = *reinterpret_cast<const float4*>(res + 4 * i);
                                 a.x += r4.x; a.y += r4.y; a.z += r4.z; a.w += r4.w;
@@ -280,6 +298,7 @@ dia_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&t_empty[acc]);
+            ++it;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -328,10 +347,11 @@ cudaError_t launch_transpose_to_bf16(const void* w, int src_bf16, void* wt, int 
     return cudaGetLastError();
 }
 
-// returns cudaErrorNotSupported for shapes the tiling does not cover (the caller decides what to do)
-cudaError_t launch_gemm_tcgen05(const float* x, const float* norm_w, float eps, const void* wt, const float* residual,
-                                float* y, void* workspace, int M, int N, int K, cudaStream_t st) {
-    if (M <= 0 || N % 4 || N <= 0 || K % BK || K < BK) return cudaErrorNotSupported;
+// A: bf16 [terms * M][K], the terms of the activation stacked (terms = 1: the activation itself); Wt: bf16 [wt_rows][K].
+// Returns cudaErrorNotSupported for shapes the tiling does not cover (the caller decides what to do).
+cudaError_t launch_gemm_tcgen05_bf16(const void* a_bf16, int terms, const void* wt, long long wt_rows, float* y, int M, int N,
+                                     int K, const GemmEpilogue& ep, const GemmGroups* groups, cudaStream_t st) {
+    if (!gemm_tcgen05_shape_ok(M, N, K) || terms < 1 || terms > kTerms || wt_rows < N) return cudaErrorNotSupported;
     static bool attr[64] = {};                         // function attributes are per device
     int dev = 0;
     cudaError_t e0 = cudaGetDevice(&dev);
@@ -341,14 +361,8 @@ cudaError_t launch_gemm_tcgen05(const float* x, const float* norm_w, float eps, 
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr[dev] = true;
     }
-    const long long n = (long long)M * K;
-    if (norm_w)
-        split3_norm_rows_kernel<<<M, 256, 0, st>>>(x, norm_w, eps, reinterpret_cast<__nv_bfloat16*>(workspace), M, K);
-    else
-        split3_rows_kernel<<<(int)std::min<long long>((n + 255) / 256, 148 * 16), 256, 0, st>>>(
-            x, reinterpret_cast<__nv_bfloat16*>(workspace), n);
     CUtensorMap ma, mb;
-    if (!make_map(&ma, workspace, (long long)kTerms * M, K, BM) || !make_map(&mb, wt, N, K, BN)) return cudaErrorNotSupported;
+    if (!make_map(&ma, a_bf16, (long long)terms * M, K, BM) || !make_map(&mb, wt, wt_rows, K, BN)) return cudaErrorNotSupported;
     static int n_sm[64] = {};
     if (dev < 0 || dev >= 64 || n_sm[dev] == 0) {
         int n = 0;
@@ -358,8 +372,24 @@ cudaError_t launch_gemm_tcgen05(const float* x, const float* norm_w, float eps, 
     }
     const int sms = (dev < 0 || dev >= 64) ? n_sm[0] : n_sm[dev];
     const int n_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
-    dia_gemm_tcgen05_kernel<<<std::min(n_tiles, sms), kGemmThreads, kGemmSmem, st>>>(ma, mb, y, residual, M, N, K);
+    dia_gemm_tcgen05_kernel<<<std::min(n_tiles, sms), kGemmThreads, kGemmSmem, st>>>(
+        ma, mb, y, ep.residual, M, N, K, terms, ep.dyt_w, ep.dyt_b, ep.dyt_alpha, groups ? groups->row_group : nullptr,
+        groups ? groups->group_rows : 0, groups ? groups->n_rows : nullptr);
     return cudaGetLastError();
+}
+
+// fp32 activations: the three-term split (with the row's RMSNorm in front when norm_w is given), then the kernel
+cudaError_t launch_gemm_tcgen05(const float* x, const float* norm_w, float eps, const void* wt, const float* residual,
+                                float* y, void* workspace, int M, int N, int K, cudaStream_t st) {
+    if (M <= 0 || N % 4 || N <= 0 || K % BK || K < BK) return cudaErrorNotSupported;
+    const long long n = (long long)M * K;
+    if (norm_w)
+        split3_norm_rows_kernel<<<M, 256, 0, st>>>(x, norm_w, eps, reinterpret_cast<__nv_bfloat16*>(workspace), M, K);
+    else
+        split3_rows_kernel<<<(int)std::min<long long>((n + 255) / 256, 148 * 16), 256, 0, st>>>(
+            x, reinterpret_cast<__nv_bfloat16*>(workspace), n);
+    const GemmEpilogue ep{residual, nullptr, nullptr, 0.f};
+    return launch_gemm_tcgen05_bf16(workspace, kTerms, wt, N, y, M, N, K, ep, nullptr, st);
 }
 
 }  // namespace dia

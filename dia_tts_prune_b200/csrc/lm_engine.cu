@@ -12,14 +12,24 @@
 //   the shared expert on h                      linear, silu_mul, linear
 //   x += norm(shared + the row's expert rows)   residual_dyt
 // and the final norm + head on the wanted rows.  Nothing here depends on how many sequences the rows belong to.
+//
+// Products.  With float32 precision every product runs on the fp32 FMA kernels.  With bfloat16 precision a step of at
+// least kTensorRowsMin rows (a prompt portion) runs its products on the tensor cores (the tcgen05 kernel of
+// gemm_tcgen05.cu, bf16 operands, fp32 accumulation in tensor memory): the norm / attention / gate kernels write the
+// bf16 operand beside their fp32 result, the expert groups are packed (gathered, scaled by the router score, padded to
+// the 128-row tile) into one bf16 operand, and the output projection's epilogue applies the DynamicTanh and adds the
+// residual stream.  Shorter steps (decoding) stream the weights once per row on the row kernels.  The router, norms,
+// scores, softmax, pages and the residual stream are fp32 in both.
 #include <algorithm>
 #include <atomic>
+#include <cstdint>
 #include <cstdio>
 #include <new>
 #include <vector>
 
 #include <cuda_runtime.h>
 
+#include "gemm_tcgen05.h"
 #include "lm_b200.h"
 #include "lm_internal.h"
 
@@ -66,15 +76,25 @@ struct lm_b200_engine {
     // workspace (fp32 unless noted)
     float *x, *h, *qk, *att, *y, *z, *sel_w, *a_scale, *gu, *mid, *parts, *sgu, *smid, *hw;
     int *sel_e, *slot_of, *a_row, *a_expert, *n_slots;
+    // bf16 operands of the tensor-core products (bfloat16 precision only)
+    void *hb, *attb, *packb, *midb, *smidb, *hwb;
 };
 
 namespace {
 
-int slots_bound(int rows, int top, int experts) {
+constexpr int kTensorRowsMin = 32;               // rows of a step from which its products run on the tensor cores
+
+// assignment slots of `rows` rows when every expert group is padded to `pad` slots
+int slots_bound(int rows, int top, int experts, int pad) {
     const int n = rows * top;
-    if (n <= lm::kRowsKernelMax) return n;
-    return n + std::min(experts, n) * (lm::kTileRows - 1);
+    return n + std::min(experts, n) * (pad - 1);
 }
+
+bool tensor_path(const lm_b200_engine* e, int M, int N, int K) {
+    return e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin && dia::gemm_tcgen05_shape_ok(M, N, K);
+}
+
+const dia::GemmEpilogue kPlain{nullptr, nullptr, nullptr, 0.f};
 
 struct StepView {
     const int *token, *want;
@@ -113,41 +133,86 @@ int norm_tapmix(lm_b200_engine* e, const lm_b200_layer& l, int sub, const float*
     const float* taps = sub ? l.tap_ff : l.tap_mix;
     float* tail = sub ? l.tail_ff : l.tail_mix;
     const int T = taps ? e->m.taps : 0;
-    LCK(lm::launch_dyt_tapmix(x, N(n), taps, T, tail, v.rm, out, M, e->m.width, st));
+    void* out_b = (e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin && out == e->h) ? e->hb : nullptr;
+    LCK(lm::launch_dyt_tapmix(x, N(n), taps, T, tail, v.rm, out, out_b, M, e->m.width, st));
     if (T > 1) LCK(lm::launch_tapmix_tail(x, N(n), T, tail, v.sm, n_seq, e->m.width, st));
     return LM_B200_OK;
 }
 
-int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const StepView& v, int M, float* y, cudaStream_t st) {
+// y = mixer(h); with fuse_x, x += norm_mix_out(y) instead (in the output projection's epilogue where that runs on the
+// tensor cores).  hb: the bf16 copy of h when the caller has one.
+int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, const StepView& v, int M, float* y,
+          float* fuse_x, cudaStream_t st) {
     const int D = e->m.width, nq = l.heads * l.dim, nk = l.kv_heads * l.dim;
     const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
-    LCK(lm::launch_linear(h, D, l.w_qk, 0, e->qk, nq + nk, M, nq + nk, D, nullptr, st));
+    if (tensor_path(e, M, nq + nk, D)) {
+        if (!hb) {
+            LCK(lm::launch_pack_rows_bf16(h, e->hb, M, D, nullptr, st));
+            hb = e->hb;
+        }
+        LCK(dia::launch_gemm_tcgen05_bf16(hb, 1, l.w_qk, nq + nk, e->qk, M, nq + nk, D, kPlain, nullptr, st));
+    } else {
+        LCK(lm::launch_linear(h, D, l.w_qk, 0, e->qk, nq + nk, M, nq + nk, D, nullptr, st));
+    }
     LCK(lm::launch_qk_norm_cache(e->qk, nq, nk, l.q_norm, l.k_norm, e->m.eps, l.k_pages, l.v_pages, pm, l.kv_heads, l.dim,
                                  v.rm, M, st));
     const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
-    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, M, st));
-    LCK(lm::launch_linear(e->att, nq, l.w_o, 0, y, D, M, D, nq, nullptr, st));
+    const bool tc_o = tensor_path(e, M, D, nq);
+    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, tc_o ? e->attb : nullptr, M, st));
+    if (tc_o) {
+        if (fuse_x) {
+            const dia::GemmEpilogue ep{fuse_x, l.norm_mix_out.w, l.norm_mix_out.b, l.norm_mix_out.alpha};
+            LCK(dia::launch_gemm_tcgen05_bf16(e->attb, 1, l.w_o, D, fuse_x, M, D, nq, ep, nullptr, st));
+            return LM_B200_OK;
+        }
+        LCK(dia::launch_gemm_tcgen05_bf16(e->attb, 1, l.w_o, D, y, M, D, nq, kPlain, nullptr, st));
+    } else {
+        LCK(lm::launch_linear(e->att, nq, l.w_o, 0, y, D, M, D, nq, nullptr, st));
+    }
+    if (fuse_x) LCK(lm::launch_residual_dyt(fuse_x, y, nullptr, nullptr, 0, N(l.norm_mix_out), M, D, st));
     return LM_B200_OK;
 }
 
 // leaves the shared expert's rows in e->y (when there is one) and the experts' rows in e->parts / e->slot_of
-int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, int M, cudaStream_t st) {
+int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, cudaStream_t st) {
     const int D = e->m.width, E = l.experts, top = l.top, F = l.expert_ff, Sf = l.shared_ff;
     LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, E, M, E, D, nullptr, st));
     LCK(lm::launch_router_topk(e->z, E, top, M, e->sel_e, e->sel_w, st));
-    const int n_assign = M * top, bound = slots_bound(M, top, E);
-    const int pad = n_assign <= lm::kRowsKernelMax ? 1 : lm::kTileRows;
+    const int n_assign = M * top;
+    // both expert products on the tensor cores, or neither: the groups are padded to the row tile of the kernel that runs
+    const bool tc = tensor_path(e, M, 2 * F, D) && tensor_path(e, M, D, F);
+    const int pad = tc ? dia::kGemmRowTile : (n_assign <= lm::kRowsKernelMax ? 1 : lm::kTileRows);
+    const int bound = slots_bound(M, top, E, pad);
     const lm::GroupMap gm{e->a_row, e->a_scale, e->a_expert, e->n_slots};
     LCK(lm::launch_moe_group(e->sel_e, e->sel_w, n_assign, top, E, pad, gm, e->slot_of, bound, st));
-    LCK(lm::launch_linear(h, D, l.w_gate_up, 2LL * F * D, e->gu, 2 * F, bound, 2 * F, D, &gm, st));
-    LCK(lm::launch_silu_mul(e->gu, e->mid, bound, F, &gm, st));
-    // the rows of mid are already in slot order: identity gather, no scale, the slots' experts
-    const lm::GroupMap gm_down{nullptr, nullptr, e->a_expert, e->n_slots};
-    LCK(lm::launch_linear(e->mid, F, l.w_down, (long long)D * F, e->parts, D, bound, D, F, &gm_down, st));
+    if (tc) {
+        LCK(lm::launch_pack_rows_bf16(h, e->packb, bound, D, &gm, st));
+        const dia::GemmGroups gu_groups{e->a_expert, 2 * F, e->n_slots}, down_groups{e->a_expert, D, e->n_slots};
+        LCK(dia::launch_gemm_tcgen05_bf16(e->packb, 1, l.w_gate_up, (long long)E * 2 * F, e->gu, bound, 2 * F, D, kPlain,
+                                          &gu_groups, st));
+        LCK(lm::launch_silu_mul(e->gu, nullptr, e->midb, bound, F, &gm, st));
+        LCK(dia::launch_gemm_tcgen05_bf16(e->midb, 1, l.w_down, (long long)E * D, e->parts, bound, D, F, kPlain, &down_groups, st));
+    } else {
+        LCK(lm::launch_linear(h, D, l.w_gate_up, 2LL * F * D, e->gu, 2 * F, bound, 2 * F, D, &gm, st));
+        LCK(lm::launch_silu_mul(e->gu, e->mid, nullptr, bound, F, &gm, st));
+        // the rows of mid are already in slot order: identity gather, no scale, the slots' experts
+        const lm::GroupMap gm_down{nullptr, nullptr, e->a_expert, e->n_slots};
+        LCK(lm::launch_linear(e->mid, F, l.w_down, (long long)D * F, e->parts, D, bound, D, F, &gm_down, st));
+    }
     if (Sf > 0) {
-        LCK(lm::launch_linear(h, D, l.ws_gate_up, 0, e->sgu, 2 * Sf, M, 2 * Sf, D, nullptr, st));
-        LCK(lm::launch_silu_mul(e->sgu, e->smid, M, Sf, nullptr, st));
-        LCK(lm::launch_linear(e->smid, Sf, l.ws_down, 0, e->y, D, M, D, Sf, nullptr, st));
+        if (tensor_path(e, M, 2 * Sf, D) && tensor_path(e, M, D, Sf)) {
+            if (!hb) {
+                LCK(lm::launch_pack_rows_bf16(h, e->hb, M, D, nullptr, st));
+                hb = e->hb;
+            }
+            LCK(dia::launch_gemm_tcgen05_bf16(hb, 1, l.ws_gate_up, 2 * Sf, e->sgu, M, 2 * Sf, D, kPlain, nullptr, st));
+            LCK(lm::launch_silu_mul(e->sgu, nullptr, e->smidb, M, Sf, nullptr, st));
+            LCK(dia::launch_gemm_tcgen05_bf16(e->smidb, 1, l.ws_down, D, e->y, M, D, Sf, kPlain, nullptr, st));
+        } else {
+            LCK(lm::launch_linear(h, D, l.ws_gate_up, 0, e->sgu, 2 * Sf, M, 2 * Sf, D, nullptr, st));
+            LCK(lm::launch_silu_mul(e->sgu, e->smid, nullptr, M, Sf, nullptr, st));
+            LCK(lm::launch_linear(e->smid, Sf, l.ws_down, 0, e->y, D, M, D, Sf, nullptr, st));
+        }
     }
     return LM_B200_OK;
 }
@@ -164,7 +229,8 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     if (!model || !layers || !out) return LM_B200_EINVAL;
     const lm_b200_model& m = *model;
     if (m.n_layer <= 0 || m.width <= 0 || m.vocab <= 0 || m.taps < 0 || m.taps > lm::kMaxTaps || m.page_size <= 0 ||
-        m.max_pages <= 0 || m.n_slots <= 0 || m.max_rows <= 0 || !m.embed || !m.head || !m.final_norm.w || !m.final_norm.b ||
+        m.max_pages <= 0 || m.n_slots <= 0 || m.max_rows <= 0 ||
+        (m.precision != LM_B200_PRECISION_FP32 && m.precision != LM_B200_PRECISION_BF16) || !m.embed || !m.head || !m.final_norm.w || !m.final_norm.b ||
         !m.page_table)
         return LM_B200_EINVAL;
     for (int i = 0; i < m.n_layer; ++i) {
@@ -188,7 +254,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
             top = std::max(top, (size_t)l.top);
             F = std::max(F, (size_t)l.expert_ff);
             Sf = std::max(Sf, (size_t)l.shared_ff);
-            slots = std::max(slots, (size_t)slots_bound(m.max_rows, l.top, l.experts));
+            slots = std::max(slots, (size_t)slots_bound(m.max_rows, l.top, l.experts, dia::kGemmRowTile));
         }
     }
     e->max_slots = (int)slots;
@@ -199,6 +265,9 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
                  o_slot_of = take(R * top * 4), o_a_row = take(slots * 4), o_a_scale = take(slots * 4),
                  o_a_expert = take(slots * 4), o_n_slots = take(4), o_gu = take(slots * 2 * F * 4), o_mid = take(slots * F * 4),
                  o_parts = take(slots * D * 4), o_sgu = take(R * 2 * Sf * 4), o_smid = take(R * Sf * 4), o_hw = take(R * D * 4);
+    const bool tcb = m.precision == LM_B200_PRECISION_BF16;
+    const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
+                 o_midb = take(tcb ? slots * F * 2 : 0), o_smidb = take(tcb ? R * Sf * 2 : 0), o_hwb = take(tcb ? R * D * 2 : 0);
     if (cudaMalloc(&e->arena, off) != cudaSuccess) {
         (void)cudaGetLastError();
         delete e;
@@ -212,6 +281,8 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->a_expert = (int*)(b + o_a_expert); e->n_slots = (int*)(b + o_n_slots); e->gu = (float*)(b + o_gu);
     e->mid = (float*)(b + o_mid); e->parts = (float*)(b + o_parts); e->sgu = (float*)(b + o_sgu);
     e->smid = (float*)(b + o_smid); e->hw = (float*)(b + o_hw);
+    e->hb = b + o_hb; e->attb = b + o_attb; e->packb = b + o_packb; e->midb = b + o_midb; e->smidb = b + o_smidb;
+    e->hwb = b + o_hwb;
     *out = e;
     return LM_B200_OK;
 }
@@ -241,13 +312,13 @@ int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, in
         const lm_b200_layer& l = e->layers[i];
         int rc = norm_tapmix(e, l, 0, e->x, v, M, n_seq, e->h, st);
         if (rc) return rc;
-        rc = mixer(e, l, e->h, v, M, e->y, st);
+        const void* hb = (e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin) ? e->hb : nullptr;
+        rc = mixer(e, l, e->h, hb, v, M, e->y, e->x, st);
         if (rc) return rc;
-        LCK(lm::launch_residual_dyt(e->x, e->y, nullptr, nullptr, 0, N(l.norm_mix_out), M, D, st));
         if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
             rc = norm_tapmix(e, l, 1, e->x, v, M, n_seq, e->h, st);
             if (rc) return rc;
-            rc = feed_forward(e, l, e->h, M, st);
+            rc = feed_forward(e, l, e->h, hb, M, st);
             if (rc) return rc;
             LCK(lm::launch_residual_dyt(e->x, l.shared_ff > 0 ? e->y : nullptr, e->parts, e->slot_of, l.top, N(l.norm_ff_out), M,
                                         D, st));
@@ -259,8 +330,12 @@ int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, in
         }
     }
     if (n_want > 0) {
-        LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, n_want, D, st));
-        LCK(lm::launch_linear(e->hw, D, e->m.head, 0, logits_out, e->m.vocab, n_want, e->m.vocab, D, nullptr, st));
+        const bool tc = tensor_path(e, n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
+        LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
+        if (tc)
+            LCK(dia::launch_gemm_tcgen05_bf16(e->hwb, 1, e->m.head, e->m.vocab, logits_out, n_want, e->m.vocab, D, kPlain, nullptr, st));
+        else
+            LCK(lm::launch_linear(e->hw, D, e->m.head, 0, logits_out, e->m.vocab, n_want, e->m.vocab, D, nullptr, st));
     }
     return LM_B200_OK;
 }
@@ -281,7 +356,7 @@ int lm_b200_op_mixer(lm_b200_engine* e, int layer, const float* h, const int32_t
         return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
-    return mixer(e, e->layers[layer], h, view(step, M, n_seq), M, y, S(stream));
+    return mixer(e, e->layers[layer], h, nullptr, view(step, M, n_seq), M, y, nullptr, S(stream));
 }
 
 int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y, void* stream) {
@@ -290,7 +365,7 @@ int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y,
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
-    const int rc = feed_forward(e, l, h, M, S(stream));
+    const int rc = feed_forward(e, l, h, nullptr, M, S(stream));
     if (rc) return rc;
     const lm::NormW none{nullptr, nullptr, 0.f};                  // plain sum, written to y
     LCK(lm::launch_residual_dyt(y, l.shared_ff > 0 ? e->y : nullptr, e->parts, e->slot_of, l.top, none, M, e->m.width, S(stream)));
@@ -300,6 +375,14 @@ int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y,
 int lm_b200_op_linear(const float* A, const void* W_bf16, float* Y, int M, int N, int K, void* stream) {
     if (!A || !W_bf16 || !Y || M <= 0 || N <= 0 || K <= 0) return LM_B200_EINVAL;
     LCK(lm::launch_linear(A, K, W_bf16, 0, Y, N, M, N, K, nullptr, S(stream)));
+    return LM_B200_OK;
+}
+
+int lm_b200_op_linear_tc(const float* A, const void* W_bf16, float* Y, void* a_bf16, int M, int N, int K, void* stream) {
+    if (!A || !W_bf16 || !Y || !a_bf16 || M <= 0 || N <= 0 || K <= 0) return LM_B200_EINVAL;
+    if (!dia::gemm_tcgen05_shape_ok(M, N, K)) return LM_B200_EUNSUPPORTED;
+    LCK(lm::launch_pack_rows_bf16(A, a_bf16, M, K, nullptr, S(stream)));
+    LCK(dia::launch_gemm_tcgen05_bf16(a_bf16, 1, W_bf16, N, Y, M, N, K, kPlain, nullptr, S(stream)));
     return LM_B200_OK;
 }
 

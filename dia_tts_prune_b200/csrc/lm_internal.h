@@ -8,7 +8,8 @@ namespace lm {
 
 constexpr int kMaxTaps = 16;          // taps of the causal tap mix (the tail keeps taps - 1 rows per sequence)
 constexpr int kRowsKernelMax = 8;     // up to this many rows a linear layer runs one warp per output element
-constexpr int kTileRows = 64;         // row tile of the tiled linear kernel = padding of an expert group
+constexpr int kTileRows = 64;         // row tile of the tiled linear kernel = padding of an expert group on that kernel
+constexpr int kAttnRowsKernelMax = 8; // up to this many rows attention runs one CTA per (row, head)
 
 struct NormW { const float* w; const float* b; float alpha; };                  // DynamicTanh: tanh(alpha x) w + b
 struct RowMeta { const int* slot; const int* pos; const int* start; };          // per row of the step
@@ -23,7 +24,7 @@ struct GroupMap { int* a_row; float* a_scale; int* a_expert; int* n_slots; };   
 
 cudaError_t launch_embed(const void* table_bf16, const int* ids, float* out, int M, int V, int D, cudaStream_t st);
 cudaError_t launch_dyt_tapmix(const float* x, const NormW& n, const float* cw, int taps, const float* tail, const RowMeta& rm,
-                              float* out, int M, int D, cudaStream_t st);
+                              float* out, void* out_bf16, int M, int D, cudaStream_t st);
 cudaError_t launch_tapmix_tail(const float* x, const NormW& n, int taps, float* tail, const SeqMeta& sm, int n_seq, int D,
                                cudaStream_t st);
 cudaError_t launch_linear(const float* A, int lda, const void* W_bf16, long long w_expert_stride, float* Y, int ldy, int M,
@@ -32,14 +33,16 @@ cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, con
                                  float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
                                  cudaStream_t st);
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
-                                  const AttnShape& a, const RowMeta& rm, float* out, int M, cudaStream_t st);
+                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, int M, cudaStream_t st);
 cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st);
 cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign, int top, int E, int pad, const GroupMap& gm,
                              int* slot_of, int max_slots, cudaStream_t st);
-cudaError_t launch_silu_mul(const float* gu, float* mid, int M, int F, const GroupMap* gm, cudaStream_t st);
+cudaError_t launch_silu_mul(const float* gu, float* mid, void* mid_bf16, int M, int F, const GroupMap* gm, cudaStream_t st);
+cudaError_t launch_pack_rows_bf16(const float* A, void* Ab, int M, int D, const GroupMap* gm, cudaStream_t st);
 cudaError_t launch_residual_dyt(float* x, const float* y, const float* parts, const int* slot_of, int top, const NormW& n, int M,
                                 int D, cudaStream_t st);
-cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, int M, int D, cudaStream_t st);
+cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, void* out_bf16, int M, int D,
+                              cudaStream_t st);
 cudaError_t launch_argmax_rows(const float* logits, int M, int V, int* out, cudaStream_t st);
 
 }  // namespace lm

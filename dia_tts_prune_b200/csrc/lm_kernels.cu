@@ -20,6 +20,8 @@
 //   qk_norm_cache_kernel       whole-projection RMS norm of q and k, raw k and normed k scattered into the paged cache
 //   sink_attention_kernel      softmax attention over the pages with per-head temperature, tanh cap, linear distance
 //                              bias, a window that keeps the first tokens, and a value-less sink term in the denominator
+//   sink_attention_tile_kernel the same for prompt portions: 64 queries share the key / value tiles (flash-style)
+//   pack_rows_bf16_kernel      the expert-grouped, score-scaled bf16 operand of the tensor-core products
 //   router_topk_kernel         sigmoid scores and the `top` best experts of every row
 //   moe_group_kernel           groups (row, expert) assignments by expert, padded to the GEMM's row tile
 //   silu_mul_kernel            silu(gate) * up on [gate | up] rows
@@ -90,7 +92,8 @@ __global__ void embed_rows_bf16_kernel(const __nv_bfloat16* __restrict__ table, 
 __global__ void dyt_tapmix_kernel(const float* __restrict__ x, const float* __restrict__ nw, const float* __restrict__ nb,
                                   float alpha, const float* __restrict__ cw, int taps, const float* __restrict__ tail,
                                   const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-                                  const int* __restrict__ row_start, float* __restrict__ out, int D) {
+                                  const int* __restrict__ row_start, float* __restrict__ out,
+                                  __nv_bfloat16* __restrict__ out_b, int D) {
     const int r = blockIdx.x;
     const int slot = row_slot[r], pos = row_pos[r], start = row_start[r];
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
@@ -107,6 +110,7 @@ __global__ void dyt_tapmix_kernel(const float* __restrict__ x, const float* __re
             acc = fmaf(cw[(size_t)c * taps + taps - 1 - o], v, acc);
         }
         out[(size_t)r * D + c] = acc;
+        if (out_b) out_b[(size_t)r * D + c] = __float2bfloat16_rn(acc);       // the tensor-core operand of the same row
     }
 }
 
@@ -310,7 +314,8 @@ sink_attention_kernel(const float* __restrict__ qk, int q_stride, const float* _
                       const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
                       int heads, int kv_heads, int dim, float scale, float cap, const float* __restrict__ temp,
                       const float* __restrict__ slopes, const float* __restrict__ sink, int window, int keep_first,
-                      const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out) {
+                      const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out,
+                      __nv_bfloat16* __restrict__ out_b) {
     extern __shared__ __align__(16) float sm[];
     float* qs = sm;                                           // [dim]
     float* ps = qs + ((dim + 3) & ~3);                        // [kAttnThreads]
@@ -392,6 +397,214 @@ sink_attention_kernel(const float* __restrict__ qk, int q_stride, const float* _
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) o += acc_s[w * dim + c];
         out[((size_t)r * heads + h) * dim + c] = o / l;
+        if (out_b) out_b[((size_t)r * heads + h) * dim + c] = __float2bfloat16_rn(o / l);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The same attention for prompt portions: one CTA per (64 consecutive rows of the step, query head), flash-style - key
+// and value tiles of 64 positions gathered from the pages into padded shared memory and shared by the 64 queries, 4 x 4
+// score blocks per thread, online softmax whose running maximum starts at the sink.  The rows of a tile may belong to
+// several sequences: a maximal run of rows with one slot and consecutive positions is a segment, the segments are
+// walked one after the other, and a row's statistics move only while its own segment is walked.  A segment's keys are
+// the kept first positions that lie in front of its window range, then the range from the first row's window start to
+// the last row; the visibility rule is applied per (query, key) pair.  NC: the head size in chunks of 64.
+constexpr int kTQ = 64, kTK = 64, kTileThreads = 256, kTPStride = 68;
+
+template <int NC>
+__global__ void __launch_bounds__(kTileThreads, 1)
+sink_attention_tile_kernel(const float* __restrict__ qk, int q_stride, const float* __restrict__ kcache,
+                           const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
+                           int heads, int kv_heads, int dim, float scale, float cap, const float* __restrict__ temp,
+                           const float* __restrict__ slopes, const float* __restrict__ sink, int window, int keep_first,
+                           const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out,
+                           __nv_bfloat16* __restrict__ out_b, int M) {
+    constexpr int DP = 64 * NC, QS = DP + 4, C4 = DP / 4;
+    extern __shared__ __align__(16) float sm[];
+    float* Qs = sm;                                           // [64][QS]
+    float* Ks = Qs + kTQ * QS;                                // [64][QS]
+    float* Vs = Ks + kTK * QS;                                // [64][DP]
+    float* Ps = Vs + kTK * DP;                                // [64][68]
+    int* s_slot = reinterpret_cast<int*>(Ps + kTQ * kTPStride);   // [64]
+    int* s_pos = s_slot + kTQ;                                // [64]
+
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int r0 = blockIdx.x * kTQ, h = blockIdx.y;
+    const int n_rows = min(kTQ, M - r0);
+    const int g = h / (heads / kv_heads);
+    const bool vec = (dim % 4) == 0 && (q_stride % 4) == 0;
+    const float mult = scale * (temp ? temp[h] : 1.f);
+    const float slope = slopes ? slopes[h] : 0.f;
+    const float sink_h = sink ? sink[h] : -CUDART_INF_F;
+
+    if (tid < kTQ) {
+        s_slot[tid] = tid < n_rows ? row_slot[r0 + tid] : -1;
+        s_pos[tid] = tid < n_rows ? row_pos[r0 + tid] : -1;
+    }
+    for (int i = tid; i < kTQ * C4; i += kTileThreads) {
+        const int r = i / C4, c = (i - r * C4) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < n_rows && c < dim) {
+            const float* src = qk + (size_t)(r0 + r) * q_stride + (size_t)h * dim + c;
+            if (vec) v = *reinterpret_cast<const float4*>(src);
+            else {
+                v.x = src[0];
+                if (c + 1 < dim) v.y = src[1];
+                if (c + 2 < dim) v.z = src[2];
+                if (c + 3 < dim) v.w = src[3];
+            }
+        }
+        *reinterpret_cast<float4*>(Qs + r * QS + c) = v;
+    }
+
+    float m_run[4], l_run[4], o[4][4 * NC];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m_run[i] = sink_h; l_run[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4 * NC; ++j) o[i][j] = 0.f;
+    }
+    __syncthreads();
+
+    int seg_a = 0;
+    while (seg_a < n_rows) {
+        int seg_b = seg_a + 1;
+        while (seg_b < n_rows && s_slot[seg_b] == s_slot[seg_a] && s_pos[seg_b] == s_pos[seg_b - 1] + 1) ++seg_b;
+        const int* pages = table + (size_t)s_slot[seg_a] * max_pages;
+        const int p_first = s_pos[seg_a], p_last = s_pos[seg_b - 1];
+        const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+        const int n_keep = window > 0 ? min(keep_first, lo) : 0;
+        for (int phase = 0; phase < 2; ++phase) {
+            const int k_begin = phase == 0 ? 0 : lo, k_end = phase == 0 ? n_keep : p_last + 1;
+            for (int j0 = k_begin; j0 < k_end; j0 += kTK) {
+                __syncthreads();                              // the previous tile is consumed
+                for (int i = tid; i < kTK * C4; i += kTileThreads) {
+                    const int r = i / C4, c = (i - r * C4) * 4, j = j0 + r;
+                    float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+                    if (j < k_end && c < dim) {
+                        const size_t at = (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim + c;
+                        if (vec) {
+                            kk = *reinterpret_cast<const float4*>(kcache + at);
+                            vv = *reinterpret_cast<const float4*>(vcache + at);
+                        } else {
+                            kk.x = kcache[at]; vv.x = vcache[at];
+                            if (c + 1 < dim) { kk.y = kcache[at + 1]; vv.y = vcache[at + 1]; }
+                            if (c + 2 < dim) { kk.z = kcache[at + 2]; vv.z = vcache[at + 2]; }
+                            if (c + 3 < dim) { kk.w = kcache[at + 3]; vv.w = vcache[at + 3]; }
+                        }
+                    }
+                    *reinterpret_cast<float4*>(Ks + r * QS + c) = kk;
+                    *reinterpret_cast<float4*>(Vs + r * DP + c) = vv;
+                }
+                __syncthreads();
+                // ---- S = Q K^T: rows ty*4 + i, keys tx + 16 j ----
+                float sc[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+#pragma unroll 4
+                for (int d4 = 0; d4 < C4; ++d4) {
+                    float4 qa[4], ka[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) qa[i] = *reinterpret_cast<const float4*>(Qs + (ty * 4 + i) * QS + d4 * 4);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) ka[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * QS + d4 * 4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            sc[i][j] = fmaf(qa[i].x, ka[j].x, sc[i][j]);
+                            sc[i][j] = fmaf(qa[i].y, ka[j].y, sc[i][j]);
+                            sc[i][j] = fmaf(qa[i].z, ka[j].z, sc[i][j]);
+                            sc[i][j] = fmaf(qa[i].w, ka[j].w, sc[i][j]);
+                        }
+                }
+                // ---- temperature, cap, distance bias, visibility; online softmax over the 16 threads of a row ----
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = ty * 4 + i;
+                    const bool live = row >= seg_a && row < seg_b;
+                    const int qi = s_pos[row];
+                    float mx = -CUDART_INF_F;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int key = j0 + tx + 16 * j;
+                        const bool ok = live && key < k_end && key <= qi && (window <= 0 || qi - key < window || key < keep_first);
+                        float v = sc[i][j] * mult;
+                        if (cap > 0.f) v = cap * tanhf(v / cap);
+                        v -= slope * (float)(qi - key);
+                        sc[i][j] = ok ? v : -CUDART_INF_F;
+                        mx = fmaxf(mx, sc[i][j]);
+                    }
+#pragma unroll
+                    for (int w = 8; w >= 1; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+                    const float m_new = fmaxf(m_run[i], mx);
+                    float corr = 1.f, psum = 0.f;
+                    if (m_new == -CUDART_INF_F) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+                    } else {
+                        corr = expf(m_run[i] - m_new);        // exp(-inf) = 0 on the first live tile without a sink
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { sc[i][j] = expf(sc[i][j] - m_new); psum += sc[i][j]; }
+                    }
+#pragma unroll
+                    for (int w = 8; w >= 1; w >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, w);
+                    l_run[i] = l_run[i] * corr + psum;
+                    m_run[i] = m_new;
+#pragma unroll
+                    for (int j = 0; j < 4 * NC; ++j) o[i][j] *= corr;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) Ps[row * kTPStride + tx + 16 * j] = sc[i][j];
+                }
+                __syncthreads();
+                // ---- O += P V: rows ty*4 + i, value columns 64 c + tx*4 .. +3 ----
+#pragma unroll 2
+                for (int c4 = 0; c4 < kTK / 4; ++c4) {
+                    float4 pa[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) pa[i] = *reinterpret_cast<const float4*>(Ps + (ty * 4 + i) * kTPStride + c4 * 4);
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            const float4 v4 = *reinterpret_cast<const float4*>(Vs + (c4 * 4 + cc) * DP + 64 * c + tx * 4);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float pv = cc == 0 ? pa[i].x : cc == 1 ? pa[i].y : cc == 2 ? pa[i].z : pa[i].w;
+                                o[i][4 * c + 0] = fmaf(pv, v4.x, o[i][4 * c + 0]);
+                                o[i][4 * c + 1] = fmaf(pv, v4.y, o[i][4 * c + 1]);
+                                o[i][4 * c + 2] = fmaf(pv, v4.z, o[i][4 * c + 2]);
+                                o[i][4 * c + 3] = fmaf(pv, v4.w, o[i][4 * c + 3]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        seg_a = seg_b;
+    }
+    // ---- the sink's own term joins the denominator; normalise and store ----
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = ty * 4 + i;
+        if (row >= n_rows) continue;
+        float l = l_run[i];
+        if (sink) l += expf(sink_h - m_run[i]);
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const size_t base = ((size_t)(r0 + row) * heads + h) * dim;
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int col = 64 * c + tx * 4 + u;
+                if (col < dim) {
+                    const float v = o[i][4 * c + u] * inv;
+                    out[base + col] = v;
+                    if (out_b) out_b[base + col] = __float2bfloat16_rn(v);
+                }
+            }
     }
 }
 
@@ -462,15 +675,34 @@ __global__ void moe_group_kernel(const int* __restrict__ sel_e, const float* __r
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict__ mid, int F, const int* __restrict__ a_row,
-                                const int* __restrict__ n_slots, int M) {
+// mid (fp32) or mid_b (bf16, the operand of a tensor-core product: padding rows are written too, as zeros)
+__global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict__ mid, __nv_bfloat16* __restrict__ mid_b, int F,
+                                const int* __restrict__ a_row, const int* __restrict__ n_slots, int M) {
     const int a = blockIdx.x;
     if (n_slots && a >= min(M, *n_slots)) return;
-    if (a_row && a_row[a] < 0) return;
+    const bool pad = a_row && a_row[a] < 0;
+    if (pad && !mid_b) return;
     for (int c = threadIdx.x; c < F; c += blockDim.x) {
-        const float g = gu[(size_t)a * 2 * F + c], u = gu[(size_t)a * 2 * F + F + c];
-        mid[(size_t)a * F + c] = (g / (1.0f + expf(-g))) * u;
+        float v = 0.f;
+        if (!pad) {
+            const float g = gu[(size_t)a * 2 * F + c], u = gu[(size_t)a * 2 * F + F + c];
+            v = (g / (1.0f + expf(-g))) * u;
+        }
+        if (mid_b) mid_b[(size_t)a * F + c] = __float2bfloat16_rn(v);
+        else mid[(size_t)a * F + c] = v;
     }
+}
+
+// Ab[a] = bf16(scale_a * A[src_a]) for the assignment slots in use, zeros for padding slots: the expert-grouped operand
+__global__ void pack_rows_bf16_kernel(const float* __restrict__ A, __nv_bfloat16* __restrict__ Ab, int D,
+                                      const int* __restrict__ a_row, const float* __restrict__ a_scale,
+                                      const int* __restrict__ n_slots, int M) {
+    const int a = blockIdx.x;
+    if (n_slots && a >= min(M, *n_slots)) return;
+    const int src = a_row ? a_row[a] : a;
+    const float sc = (a_scale && src >= 0) ? a_scale[a] : 1.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x)
+        Ab[(size_t)a * D + c] = __float2bfloat16_rn(src >= 0 ? A[(size_t)src * D + c] * sc : 0.f);
 }
 
 // x[r] += DynamicTanh(y[r] + sum_t parts[slot_of[r * top + t]])   (y or parts may be absent)
@@ -488,10 +720,14 @@ __global__ void residual_dyt_kernel(float* __restrict__ x, const float* __restri
 }
 
 __global__ void dyt_gather_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ nw,
-                                  const float* __restrict__ nb, float alpha, float* __restrict__ out, int D) {
+                                  const float* __restrict__ nb, float alpha, float* __restrict__ out,
+                                  __nv_bfloat16* __restrict__ out_b, int D) {
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
-    for (int c = threadIdx.x; c < D; c += blockDim.x)
-        out[(size_t)blockIdx.x * D + c] = dyt(x[(size_t)r * D + c], alpha, nw[c], nb[c]);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = dyt(x[(size_t)r * D + c], alpha, nw[c], nb[c]);
+        out[(size_t)blockIdx.x * D + c] = v;
+        if (out_b) out_b[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(v);
+    }
 }
 
 // greedy sampling: index of the largest logit of every row (ties: the lowest index)
@@ -529,9 +765,9 @@ cudaError_t launch_embed(const void* table, const int* ids, float* out, int M, i
 static inline int col_blocks(int D) { return D > 1024 ? (D + 1023) / 1024 : 1; }
 
 cudaError_t launch_dyt_tapmix(const float* x, const NormW& n, const float* cw, int taps, const float* tail, const RowMeta& rm,
-                              float* out, int M, int D, cudaStream_t st) {
+                              float* out, void* out_bf16, int M, int D, cudaStream_t st) {
     dyt_tapmix_kernel<<<dim3(M, col_blocks(D)), 256, 0, st>>>(x, n.w, n.b, n.alpha, cw, taps, tail, rm.slot, rm.pos, rm.start,
-                                                              out, D);
+                                                              out, reinterpret_cast<__nv_bfloat16*>(out_bf16), D);
     return cudaGetLastError();
 }
 
@@ -566,13 +802,44 @@ cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, con
     return cudaGetLastError();
 }
 
+template <int NC>
+static cudaError_t launch_attention_tiles(const float* qk, int q_stride, const float* kcache, const float* vcache,
+                                          const PageMap& pm, const AttnShape& a, const RowMeta& rm, float* out,
+                                          __nv_bfloat16* out_b, int M, cudaStream_t st) {
+    constexpr int DP = 64 * NC;
+    const size_t smem = (size_t)(2 * kTQ * (DP + 4) + kTK * DP + kTQ * kTPStride) * sizeof(float) + 2 * kTQ * sizeof(int);
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !attr[dev]) {
+        e = cudaFuncSetAttribute(sink_attention_tile_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr[dev] = true;
+    }
+    sink_attention_tile_kernel<NC><<<dim3((M + kTQ - 1) / kTQ, a.heads), kTileThreads, smem, st>>>(
+        qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
+        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, out, out_b, M);
+    return cudaGetLastError();
+}
+
+// a step of a few rows (decoding) runs one CTA per (row, head); longer steps the tiled kernel
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
-                                  const AttnShape& a, const RowMeta& rm, float* out, int M, cudaStream_t st) {
+                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, int M, cudaStream_t st) {
     if (a.dim > 32 * kAttnMaxDimPerLane || a.heads % a.kv_heads) return cudaErrorNotSupported;
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+    if (M > kAttnRowsKernelMax) {
+        switch ((a.dim + 63) / 64) {
+            case 1: return launch_attention_tiles<1>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, st);
+            case 2: return launch_attention_tiles<2>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, st);
+            case 3: return launch_attention_tiles<3>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, st);
+            default: return launch_attention_tiles<4>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, st);
+        }
+    }
     const size_t smem = (size_t)(((a.dim + 3) & ~3) + kAttnThreads + kAttnWarps * a.dim) * sizeof(float);
     sink_attention_kernel<<<dim3(M, a.heads), kAttnThreads, smem, st>>>(
         qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
-        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, out);
+        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, out, ob);
     return cudaGetLastError();
 }
 
@@ -588,8 +855,15 @@ cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign,
     return cudaGetLastError();
 }
 
-cudaError_t launch_silu_mul(const float* gu, float* mid, int M, int F, const GroupMap* gm, cudaStream_t st) {
-    silu_mul_kernel<<<M, 256, 0, st>>>(gu, mid, F, gm ? gm->a_row : nullptr, gm ? gm->n_slots : nullptr, M);
+cudaError_t launch_silu_mul(const float* gu, float* mid, void* mid_bf16, int M, int F, const GroupMap* gm, cudaStream_t st) {
+    silu_mul_kernel<<<M, 256, 0, st>>>(gu, mid, reinterpret_cast<__nv_bfloat16*>(mid_bf16), F, gm ? gm->a_row : nullptr,
+                                       gm ? gm->n_slots : nullptr, M);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pack_rows_bf16(const float* A, void* Ab, int M, int D, const GroupMap* gm, cudaStream_t st) {
+    pack_rows_bf16_kernel<<<M, 256, 0, st>>>(A, reinterpret_cast<__nv_bfloat16*>(Ab), D, gm ? gm->a_row : nullptr,
+                                             gm ? gm->a_scale : nullptr, gm ? gm->n_slots : nullptr, M);
     return cudaGetLastError();
 }
 
@@ -599,8 +873,9 @@ cudaError_t launch_residual_dyt(float* x, const float* y, const float* parts, co
     return cudaGetLastError();
 }
 
-cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, int M, int D, cudaStream_t st) {
-    dyt_gather_kernel<<<M, 256, 0, st>>>(x, rows, n.w, n.b, n.alpha, out, D);
+cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, void* out_bf16, int M, int D,
+                              cudaStream_t st) {
+    dyt_gather_kernel<<<M, 256, 0, st>>>(x, rows, n.w, n.b, n.alpha, out, reinterpret_cast<__nv_bfloat16*>(out_bf16), D);
     return cudaGetLastError();
 }
 

@@ -26,7 +26,8 @@ def launch_count() -> int:
 
 class LMEngine:
     def __init__(self, layers: list[MixLayer], embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh, *,
-                 width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024):
+                 width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024,
+                 precision: str = "bfloat16"):
         if not torch.cuda.is_available():
             raise RuntimeError("the language-model path needs a CUDA device (sm_100a); there is no CPU fallback")
         self.lib = _lm_lib.load()
@@ -44,6 +45,10 @@ class LMEngine:
         m.n_layer, m.width, m.vocab, m.taps = len(layers), self.width, self.vocab, int(taps)
         m.page_size, m.max_pages, m.n_slots, m.max_rows = state.page_size, state.max_pages, state.n_slots, self.max_rows
         m.eps = float(eps)
+        if precision not in ("bfloat16", "float32"):
+            raise ValueError("precision must be 'bfloat16' or 'float32'")
+        self.precision = precision
+        m.precision = _lm_lib.PRECISION_BF16 if precision == "bfloat16" else _lm_lib.PRECISION_FP32
         m.embed, m.head = self.embed.data_ptr(), self.head.data_ptr()
         final_norm.fill(m.final_norm)
         m.page_table = state.page_table.data_ptr()
@@ -170,12 +175,18 @@ class LMEngine:
         return y
 
 
-def linear(a: torch.Tensor, w_bf16: torch.Tensor) -> torch.Tensor:
-    """``a [M, K] float32 @ w [N, K]^T bfloat16`` on the path's own linear kernels."""
+def linear(a: torch.Tensor, w_bf16: torch.Tensor, tensor_cores: bool = False) -> torch.Tensor:
+    """``a [M, K] float32 @ w [N, K]^T bfloat16`` on the path's own linear kernels: fp32 FMA arithmetic, or (with
+    ``tensor_cores``) ``a`` rounded to bfloat16 and the tcgen05 kernel."""
     lib = _lm_lib.load()
     a = a.to(torch.float32).contiguous()
     w = w_bf16.to(torch.bfloat16).contiguous()
     y = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float32, device=a.device)
+    if tensor_cores:
+        ab = torch.empty(a.shape, dtype=torch.bfloat16, device=a.device)
+        _lm_lib.check(lib.lm_b200_op_linear_tc(a.data_ptr(), w.data_ptr(), y.data_ptr(), ab.data_ptr(), a.shape[0], w.shape[0],
+                                               a.shape[1], _stream(a.device)), "op_linear_tc")
+        return y
     _lm_lib.check(lib.lm_b200_op_linear(a.data_ptr(), w.data_ptr(), y.data_ptr(), a.shape[0], w.shape[0], a.shape[1],
                                         _stream(a.device)), "op_linear")
     return y

@@ -157,10 +157,11 @@ class CausalLM:
         self.state = PagedState([(lc.mixer.kv_heads, lc.mixer.dim) for lc in cfg.layers], cfg.width, cfg.canon.taps,
                                 max_tokens, self.device, page_size=page_size, max_sequences=max_sequences,
                                 max_sequence_tokens=max_sequence_tokens)
-        # Both dtypes keep activations, norms, scores and pages in float32 and the matrices in bfloat16 (as stored), the
-        # precision split of this framework's other model; float32 is therefore exact 32-bit arithmetic on the stored weights.
+        # float32: every product is fp32 arithmetic on the stored (bfloat16) weights.  bfloat16: the products of prompt
+        # portions run on the tensor cores with bfloat16 operands and fp32 accumulation.  Norms, scores, the router, the
+        # pages and the residual stream are float32 in both.
         self.engine = LMEngine(self.layers, weights["embed"], weights["head"], final_norm, width=cfg.width, vocab=cfg.vocab,
-                               taps=cfg.canon.taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows)
+                               taps=cfg.canon.taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype)
         self._draws = 0
 
     @classmethod

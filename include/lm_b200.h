@@ -6,8 +6,8 @@
  *
  * A model is a stack of layers  x += norm_b(mixer(tapmix(norm_a(x))));  x += norm_b'(ff(tapmix'(norm_a'(x))))  described
  * by lm_b200_layer records: the mechanisms are selected and parameterised per layer, so another design can combine them
- * differently.  Matrices are bf16 [out][in]; vectors and scalars fp32.  Activations, the residual stream, norms, the
- * router, attention scores and the K/V pages are fp32.
+ * differently.  Matrices are bf16 [out][in]; vectors and scalars fp32.  The residual stream, norms, the router,
+ * attention scores and the K/V pages are fp32; the operands of the matrix products are fp32 or bf16 (lm_b200_precision).
  *
  * A step is a flat batch of M rows (the new tokens of the scheduled sequences, the rows of one sequence adjacent and in
  * order) described by one int32 device buffer:
@@ -31,6 +31,9 @@ enum lm_b200_status { LM_B200_OK = 0, LM_B200_EINVAL = -1, LM_B200_ECUDA = -2, L
 
 enum lm_b200_mixer_kind { LM_B200_MIXER_SINK_ATTENTION = 1 };
 enum lm_b200_ff_kind { LM_B200_FF_NONE = 0, LM_B200_FF_ROUTED_EXPERTS = 1 };
+/* FP32: every product is fp32 FMA arithmetic on the stored weights.  BF16: the products of a long step (a prompt portion)
+ * run on the tensor cores with bf16 operands and fp32 accumulation; everything else stays fp32. */
+enum lm_b200_precision { LM_B200_PRECISION_FP32 = 0, LM_B200_PRECISION_BF16 = 1 };
 
 /* DynamicTanh norm: y = tanh(alpha x) w + b */
 typedef struct lm_b200_norm {
@@ -64,7 +67,7 @@ typedef struct lm_b200_model {
     int32_t n_layer, width, vocab, taps;
     int32_t page_size, max_pages, n_slots, max_rows; /* max_pages: per sequence; max_rows: rows of one forward call */
     float eps;                     /* inside the root of every RMS norm */
-    int32_t reserved;
+    int32_t precision;             /* lm_b200_precision */
     const void *embed, *head;      /* [vocab][width] */
     lm_b200_norm final_norm;
     const int32_t *page_table;     /* device, [n_slots][max_pages] */
@@ -99,6 +102,9 @@ int lm_b200_op_mixer(lm_b200_engine *e, int layer, const float *h, const int32_t
 int lm_b200_op_ff(lm_b200_engine *e, int layer, const float *h, int M, float *y, void *stream);
 /* Y[M][N] = A[M][K] . W[N][K]^T */
 int lm_b200_op_linear(const float *A, const void *W_bf16, float *Y, int M, int N, int K, void *stream);
+/* the same on the tensor cores: A is rounded to bf16 into a_bf16 [M][K] first.  K a multiple of 8, N of 4, else
+ * LM_B200_EUNSUPPORTED */
+int lm_b200_op_linear_tc(const float *A, const void *W_bf16, float *Y, void *a_bf16, int M, int N, int K, void *stream);
 /* greedy sampling: out[r] = index of the largest of logits[r][0 .. V) (ties: the lowest index) */
 int lm_b200_argmax_rows(const float *logits, int M, int V, int32_t *out, void *stream);
 

@@ -345,6 +345,6 @@ def test_registry_loads_a_model_folder_and_the_cli_entry(tmp_path):
     w = O.random_weights(cfg, 30)
     (tmp_path / "config.json").write_text(json.dumps(cfg))
     save_safetensors(tmp_path / "model.safetensors", {k: v.to(torch.bfloat16) for k, v in w.items()})
-    model = load_model(tmp_path, dtype="bfloat16", max_tokens=128)
+    model = load_model(tmp_path, dtype="float32", max_tokens=128)
     toks = tokens(cfg, 40, 31)
     close(whole(model, "r", toks), O.forward(cfg, w, toks, dtype=torch.float64))
