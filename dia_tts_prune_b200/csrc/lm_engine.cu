@@ -12,6 +12,10 @@
 //   the shared expert on h                      linear, silu_mul, linear
 //   x += norm(shared + the row's expert rows)   residual_dyt
 // and the final norm + head on the wanted rows.  Nothing here depends on how many sequences the rows belong to.
+// A step of a few rows (decoding) runs the same arithmetic in fewer launches: norm + taps + tail in one, the output
+// projection with the norm and residual add in its epilogue, router + top experts in one, the gate inside the gate | up
+// product, and one kernel for the down products of a row's experts and the shared expert, their sum, the norm and the
+// residual add.
 //
 // Products.  With float32 precision every product runs on the fp32 FMA kernels.  With bfloat16 precision a step of at
 // least kTensorRowsMin rows (a prompt portion) runs its products on the tensor cores (the tcgen05 kernel of
@@ -133,6 +137,10 @@ int norm_tapmix(lm_b200_engine* e, const lm_b200_layer& l, int sub, const float*
     const float* taps = sub ? l.tap_ff : l.tap_mix;
     float* tail = sub ? l.tail_ff : l.tail_mix;
     const int T = taps ? e->m.taps : 0;
+    if (M <= lm::kRowsKernelMax) {                   // a few rows: norm, taps and the tail update in one launch
+        LCK(lm::launch_dyt_tapmix_seq(x, N(n), taps, T, tail, v.sm, v.rm, n_seq, out, e->m.width, st));
+        return LM_B200_OK;
+    }
     void* out_b = (e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin && out == e->h) ? e->hb : nullptr;
     LCK(lm::launch_dyt_tapmix(x, N(n), taps, T, tail, v.rm, out, out_b, M, e->m.width, st));
     if (T > 1) LCK(lm::launch_tapmix_tail(x, N(n), T, tail, v.sm, n_seq, e->m.width, st));
@@ -166,6 +174,9 @@ int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void*
             return LM_B200_OK;
         }
         LCK(dia::launch_gemm_tcgen05_bf16(e->attb, 1, l.w_o, D, y, M, D, nq, kPlain, nullptr, st));
+    } else if (fuse_x && M <= lm::kRowsKernelMax) {
+        LCK(lm::launch_linear_rows_residual(e->att, nq, l.w_o, fuse_x, M, D, nq, N(l.norm_mix_out), st));
+        return LM_B200_OK;
     } else {
         LCK(lm::launch_linear(e->att, nq, l.w_o, 0, y, D, M, D, nq, nullptr, st));
     }
@@ -173,15 +184,28 @@ int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void*
     return LM_B200_OK;
 }
 
-// leaves the shared expert's rows in e->y (when there is one) and the experts' rows in e->parts / e->slot_of
-int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, cudaStream_t st) {
+// x += norm(ff(h)) with a norm, x = ff(h) without.  A few rows: router + top experts + maps, gated products, and the
+// sum over the row's experts with the norm and the residual add, four launches.  Longer steps group the (row, expert)
+// assignments by expert for the tiled products.
+int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, float* x,
+                 const lm_b200_norm* norm, cudaStream_t st) {
     const int D = e->m.width, E = l.experts, top = l.top, F = l.expert_ff, Sf = l.shared_ff;
+    const lm::NormW nrm = norm ? N(*norm) : lm::NormW{nullptr, nullptr, 0.f};
+    if (M <= lm::kRowsKernelMax) {
+        const lm::GroupMap rows{e->a_row, e->a_scale, e->a_expert, e->n_slots};
+        LCK(lm::launch_router_rows(h, D, l.w_router, E, top, M, e->z, rows, e->slot_of, st));
+        LCK(lm::launch_gated_rows(h, D, l.w_gate_up, 2LL * F * D, e->mid, M * top, F, D, &rows, st));
+        if (Sf > 0) LCK(lm::launch_gated_rows(h, D, l.ws_gate_up, 0, e->smid, M, Sf, D, nullptr, st));
+        LCK(lm::launch_down_combine_rows(e->mid, F, l.w_down, e->a_expert, top, Sf > 0 ? e->smid : nullptr, Sf, l.ws_down, x, M, D,
+                                         nrm, st));
+        return LM_B200_OK;
+    }
     LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, E, M, E, D, nullptr, st));
     LCK(lm::launch_router_topk(e->z, E, top, M, e->sel_e, e->sel_w, st));
     const int n_assign = M * top;
     // both expert products on the tensor cores, or neither: the groups are padded to the row tile of the kernel that runs
     const bool tc = tensor_path(e, M, 2 * F, D) && tensor_path(e, M, D, F);
-    const int pad = tc ? dia::kGemmRowTile : (n_assign <= lm::kRowsKernelMax ? 1 : lm::kTileRows);
+    const int pad = tc ? dia::kGemmRowTile : lm::kTileRows;
     const int bound = slots_bound(M, top, E, pad);
     const lm::GroupMap gm{e->a_row, e->a_scale, e->a_expert, e->n_slots};
     LCK(lm::launch_moe_group(e->sel_e, e->sel_w, n_assign, top, E, pad, gm, e->slot_of, bound, st));
@@ -214,6 +238,7 @@ int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
             LCK(lm::launch_linear(e->smid, Sf, l.ws_down, 0, e->y, D, M, D, Sf, nullptr, st));
         }
     }
+    LCK(lm::launch_residual_dyt(x, Sf > 0 ? e->y : nullptr, e->parts, e->slot_of, top, nrm, M, D, st));
     return LM_B200_OK;
 }
 
@@ -318,10 +343,8 @@ int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, in
         if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
             rc = norm_tapmix(e, l, 1, e->x, v, M, n_seq, e->h, st);
             if (rc) return rc;
-            rc = feed_forward(e, l, e->h, hb, M, st);
+            rc = feed_forward(e, l, e->h, hb, M, e->x, &l.norm_ff_out, st);
             if (rc) return rc;
-            LCK(lm::launch_residual_dyt(e->x, l.shared_ff > 0 ? e->y : nullptr, e->parts, e->slot_of, l.top, N(l.norm_ff_out), M,
-                                        D, st));
         }
         if (layers_out) {
             if (cudaMemcpyAsync(layers_out + (size_t)i * M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, st) !=
@@ -365,11 +388,7 @@ int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y,
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
-    const int rc = feed_forward(e, l, h, nullptr, M, S(stream));
-    if (rc) return rc;
-    const lm::NormW none{nullptr, nullptr, 0.f};                  // plain sum, written to y
-    LCK(lm::launch_residual_dyt(y, l.shared_ff > 0 ? e->y : nullptr, e->parts, e->slot_of, l.top, none, M, e->m.width, S(stream)));
-    return LM_B200_OK;
+    return feed_forward(e, l, h, nullptr, M, y, nullptr, S(stream));                // no norm: the plain sum, written to y
 }
 
 int lm_b200_op_linear(const float* A, const void* W_bf16, float* Y, int M, int N, int K, void* stream) {

@@ -29,6 +29,17 @@ cudaError_t launch_tapmix_tail(const float* x, const NormW& n, int taps, float* 
                                cudaStream_t st);
 cudaError_t launch_linear(const float* A, int lda, const void* W_bf16, long long w_expert_stride, float* Y, int ldy, int M,
                           int N, int K, const GroupMap* gm, cudaStream_t st);
+// the fused forms for a step of at most kRowsKernelMax rows
+cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* cw, int taps, float* tail, const SeqMeta& sm,
+                                  const RowMeta& rm, int n_seq, float* out, int D, cudaStream_t st);
+cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
+                                        cudaStream_t st);
+cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int M, int F, int K,
+                              const GroupMap* gm, cudaStream_t st);
+cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
+                                     int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, cudaStream_t st);
+cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
+                               int* slot_of, cudaStream_t st);
 cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,
                                  float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
                                  cudaStream_t st);

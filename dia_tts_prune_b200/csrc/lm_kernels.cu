@@ -16,7 +16,12 @@
 //                              identity added), previous inputs from the step itself or from the sequence's tail state
 //   tapmix_tail_kernel         keeps the last taps-1 normed inputs of every scheduled sequence
 //   linear_tile_kernel         Y = A . W^T, 64 x 64 x 16 tiles of fp32 FMAs, optional row gather / scale / per-tile expert
-//   linear_rows_kernel         the same interface for a handful of rows: one warp per output element
+//   linear_rows_kernel         the same interface for a handful of rows: one warp per output element; optional
+//                              DynamicTanh + residual-add epilogue
+//   dyt_tapmix_seq_kernel      norm + tap mix + tail update in one launch for a handful of rows
+//   gated_rows_kernel          silu(gate) * up inside the [gate | up] product of a handful of rows / assignments
+//   down_combine_rows_kernel   down products of a row's experts and the shared expert, their sum, norm, residual add
+//   router_rows_kernel         router logits, top experts, scores and the assignment maps of a handful of rows
 //   qk_norm_cache_kernel       whole-projection RMS norm of q and k, raw k and normed k scattered into the paged cache
 //   sink_attention_kernel      softmax attention over the pages with per-head temperature, tanh cap, linear distance
 //                              bias, a window that keeps the first tokens, and a value-less sink term in the denominator
@@ -139,6 +144,49 @@ __global__ void tapmix_tail_kernel(const float* __restrict__ x, const float* __r
     }
 }
 
+// Both of the above in one launch for a step of a few rows: one thread per (scheduled sequence, channel) walks the
+// sequence's rows in order with the last taps-1 normed inputs in registers, and leaves them as the new tail.  Same
+// operations in the same order as dyt_tapmix_kernel, so the two give the same bits.
+__global__ void dyt_tapmix_seq_kernel(const float* __restrict__ x, const float* __restrict__ nw, const float* __restrict__ nb,
+                                      float alpha, const float* __restrict__ cw, int taps, float* __restrict__ tail,
+                                      const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                                      const int* __restrict__ seq_count, const int* __restrict__ row_pos,
+                                      float* __restrict__ out, int D) {
+    const int s = blockIdx.x, T1 = taps > 0 ? taps - 1 : 0;
+    const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s];
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
+        const float w = nw[c], b = nb[c];
+        float prev[kMaxTaps];                                 // prev[o - 1]: the normed input o positions back
+        float* t = tail + (size_t)slot * T1 * D + c;
+#pragma unroll
+        for (int o = 1; o < kMaxTaps; ++o) {
+            if (o > T1) break;
+            prev[o - 1] = t[(size_t)(T1 - o) * D];
+        }
+        for (int q = 0; q < n; ++q) {
+            const int pos = row_pos[row0 + q];
+            const float cur = dyt(x[(size_t)(row0 + q) * D + c], alpha, w, b);
+            float acc = cur;
+            if (taps > 0) acc = fmaf(cw[(size_t)c * taps + taps - 1], cur, acc);
+#pragma unroll
+            for (int o = 1; o < kMaxTaps; ++o) {
+                if (o > T1 || pos - o < 0) break;
+                acc = fmaf(cw[(size_t)c * taps + taps - 1 - o], prev[o - 1], acc);
+            }
+            out[(size_t)(row0 + q) * D + c] = acc;
+#pragma unroll
+            for (int o = kMaxTaps - 1; o >= 2; --o)
+                if (o <= T1) prev[o - 1] = prev[o - 2];
+            if (T1 >= 1) prev[0] = cur;
+        }
+#pragma unroll
+        for (int o = 1; o < kMaxTaps; ++o) {
+            if (o > T1) break;
+            t[(size_t)(T1 - o) * D] = prev[o - 1];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Y[a][n] = sum_k scale_a * A[src_a][k] * W_e[n][k].  Without the maps: src_a = a, scale 1, expert 0.  With them
 // (expert groups): a indexes padded assignment slots, a_row[a] < 0 is padding, the expert of a tile is a_expert of its
@@ -230,22 +278,11 @@ linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     }
 }
 
-// one warp per output element (a, n); for a few rows (decoding): the weights stream once per row, 16 bytes per lane
-__global__ void __launch_bounds__(256)
-linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
-                   float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
-                   const float* __restrict__ a_scale, const int* __restrict__ a_expert, const int* __restrict__ n_slots) {
-    const int a = blockIdx.y;
-    const int m_end = n_slots ? min(M, *n_slots) : M;
-    if (a >= m_end) return;
-    const int src = a_row ? a_row[a] : a;
-    if (src < 0) return;
-    const int lane = threadIdx.x & 31;
-    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (n >= N) return;
-    const float sc = a_scale ? a_scale[a] : 1.f;
-    const float* arow = A + (size_t)src * lda;
-    const __nv_bfloat16* wrow = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
+// ---- the row kernels: a step of a few rows (decoding).  One warp per output element; the weights stream once per row,
+// 16 bytes per lane.  Their epilogues do what the next kernel of a long step would: the DynamicTanh + residual add, the
+// gate, the sum over a row's experts.
+__device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const __nv_bfloat16* __restrict__ wrow, int K, int lda,
+                                          float sc, int lane) {
     float acc = 0.f;
     const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(arow) & 15) == 0);
@@ -267,8 +304,113 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     } else {
         for (int k = lane; k < K; k += 32) acc = fmaf(arow[k] * sc, bf(wrow[k]), acc);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) Y[(size_t)a * ldy + n] = acc;
+    return warp_sum(acc);
+}
+
+// Y[a][n] = dot, or with res_x: res_x[a][n] += DynamicTanh(dot) (the residual stream takes the sublayer's output)
+__global__ void __launch_bounds__(256)
+linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
+                   float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
+                   const float* __restrict__ a_scale, const int* __restrict__ a_expert, const int* __restrict__ n_slots,
+                   float* __restrict__ res_x, const float* __restrict__ nw, const float* __restrict__ nb, float alpha) {
+    const int a = blockIdx.y;
+    const int m_end = n_slots ? min(M, *n_slots) : M;
+    if (a >= m_end) return;
+    const int src = a_row ? a_row[a] : a;
+    if (src < 0) return;
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const float sc = a_scale ? a_scale[a] : 1.f;
+    const __nv_bfloat16* wrow = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
+    const float acc = warp_dot(A + (size_t)src * lda, wrow, K, lda, sc, lane);
+    if (lane == 0) {
+        if (res_x) res_x[(size_t)a * ldy + n] += dyt(acc, alpha, nw[n], nb[n]);
+        else Y[(size_t)a * ldy + n] = acc;
+    }
+}
+
+// mid[a][n] = silu(A_a . Wg_e[n]) * (A_a . Wu_e[n]),  W_e = [gate rows (F) | up rows (F)][K];  a: assignment slots (with
+// the maps) or rows
+__global__ void __launch_bounds__(256)
+gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
+                  float* __restrict__ mid, int M, int F, int K, const int* __restrict__ a_row, const float* __restrict__ a_scale,
+                  const int* __restrict__ a_expert) {
+    const int a = blockIdx.y;
+    const int src = a_row ? a_row[a] : a;
+    if (src < 0) return;
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= F) return;
+    const float sc = a_scale ? a_scale[a] : 1.f;
+    const __nv_bfloat16* wg = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
+    const float* arow = A + (size_t)src * lda;
+    const float g = warp_dot(arow, wg, K, lda, sc, lane);
+    const float u = warp_dot(arow, wg + (size_t)F * K, K, lda, sc, lane);
+    if (lane == 0) mid[(size_t)a * F + n] = (g / (1.0f + expf(-g))) * u;
+}
+
+// v = smid[r] . Wsd[n] (with a shared expert) + sum_t mid[r * top + t] . Wd_{e(r, t)}[n];  x[r][n] += DynamicTanh(v), or
+// x[r][n] = v without a norm
+__global__ void __launch_bounds__(256)
+down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat16* __restrict__ Wd, const int* __restrict__ a_expert,
+                         int top, const float* __restrict__ smid, int Sf, const __nv_bfloat16* __restrict__ Wsd,
+                         float* __restrict__ x, int D, const float* __restrict__ nw, const float* __restrict__ nb, float alpha) {
+    const int r = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= D) return;
+    float v = 0.f;
+    if (smid) v = warp_dot(smid + (size_t)r * Sf, Wsd + (size_t)n * Sf, Sf, Sf, 1.f, lane);
+    for (int t = 0; t < top; ++t) {
+        const int a = r * top + t;
+        v += warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
+    }
+    if (lane == 0) {
+        if (nw) x[(size_t)r * D + n] += dyt(v, alpha, nw[n], nb[n]);
+        else x[(size_t)r * D + n] = v;
+    }
+}
+
+// One CTA per row: router logits z = h . Wr^T (fp32), the `top` largest in descending order (ties: the lower index),
+// scores sigmoid(z), and the assignment maps of the row kernels: slot r * top + t holds (row r, expert, score).
+__global__ void __launch_bounds__(128)
+router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __restrict__ Wr, int E, int top,
+                   float* __restrict__ z_out, int* __restrict__ a_row, float* __restrict__ a_scale, int* __restrict__ a_expert,
+                   int* __restrict__ slot_of, int* __restrict__ n_slots) {
+    extern __shared__ float zs[];                             // [E]
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nwarp) {
+        const float z = warp_dot(h + (size_t)r * D, Wr + (size_t)e * D, D, D, 1.f, lane);
+        if (lane == 0) { zs[e] = z; z_out[(size_t)r * E + e] = z; }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (r == 0 && lane == 0) *n_slots = gridDim.x * top;
+    for (int t = 0; t < top; ++t) {
+        float best = -CUDART_INF_F;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            bool taken = false;
+            for (int u = 0; u < t; ++u) taken |= (a_expert[r * top + u] == e);
+            const float v = zs[e];
+            if (!taken && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            const int a = r * top + t;
+            a_row[a] = r;
+            a_expert[a] = bi;
+            a_scale[a] = 1.0f / (1.0f + expf(-best));
+            slot_of[a] = a;
+        }
+        __syncwarp();
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -787,10 +929,48 @@ cudaError_t launch_linear(const float* A, int lda, const void* W, long long w_ex
     const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
     if (M <= kRowsKernelMax)
         linear_rows_kernel<<<dim3((N + 7) / 8, M), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N, K, a_row, a_scale,
-                                                                 a_expert, n_slots);
+                                                                 a_expert, n_slots, nullptr, nullptr, nullptr, 0.f);
     else
         linear_tile_kernel<<<dim3((N + BN - 1) / BN, (M + BM - 1) / BM), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N,
                                                                                       K, a_row, a_scale, a_expert, n_slots);
+    return cudaGetLastError();
+}
+
+// ---- the fused forms for a step of a few rows ----
+cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* cw, int taps, float* tail, const SeqMeta& sm,
+                                  const RowMeta& rm, int n_seq, float* out, int D, cudaStream_t st) {
+    dyt_tapmix_seq_kernel<<<dim3(n_seq, (D + 127) / 128), 128, 0, st>>>(x, n.w, n.b, n.alpha, cw, taps, tail, sm.slot, sm.row0,
+                                                                        sm.count, rm.pos, out, D);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
+                                        cudaStream_t st) {
+    linear_rows_kernel<<<dim3((N + 7) / 8, M), 256, 0, st>>>(A, lda, reinterpret_cast<const __nv_bfloat16*>(W), 0, nullptr, N, M, N,
+                                                             K, nullptr, nullptr, nullptr, nullptr, x, n.w, n.b, n.alpha);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int M, int F, int K,
+                              const GroupMap* gm, cudaStream_t st) {
+    gated_rows_kernel<<<dim3((F + 7) / 8, M), 256, 0, st>>>(A, lda, reinterpret_cast<const __nv_bfloat16*>(W), w_expert_stride, mid,
+                                                            M, F, K, gm ? gm->a_row : nullptr, gm ? gm->a_scale : nullptr,
+                                                            gm ? gm->a_expert : nullptr);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
+                                     int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, cudaStream_t st) {
+    down_combine_rows_kernel<<<dim3((D + 7) / 8, M), 256, 0, st>>>(mid, F, reinterpret_cast<const __nv_bfloat16*>(Wd), a_expert, top,
+                                                                   smid, Sf, reinterpret_cast<const __nv_bfloat16*>(Wsd), x, D, n.w,
+                                                                   n.b, n.alpha);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
+                               int* slot_of, cudaStream_t st) {
+    router_rows_kernel<<<M, 128, E * sizeof(float), st>>>(h, D, reinterpret_cast<const __nv_bfloat16*>(Wr), E, top, z, gm.a_row,
+                                                          gm.a_scale, gm.a_expert, slot_of, gm.n_slots);
     return cudaGetLastError();
 }
 
