@@ -481,6 +481,162 @@ def run_batch(args) -> None:
         dist.destroy_process_group()
 
 
+
+# ---- --lm: the decoder-only language-model path at layer sizes of a real model, beside Dia's kernels at equal size ------
+LM_SIZES = {
+    # width 2048, 16 x 128 query heads over 4 key/value heads: the shape of Dia-1.6B's decoder self-attention; two routed
+    # experts of 2048 + a shared one of 4096 = 8192 active hidden units per token, the width of Dia's decoder MLP
+    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, experts=8, top=2, expert_ff=2048, shared_ff=4096,
+                  vocab=32768, window=1024, keep_first=4),
+    "w1024": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, experts=16, top=2, expert_ff=512, shared_ff=1024,
+                  vocab=16384, window=512, keep_first=4),
+}
+
+
+def _event_ms(fn, warmup: int, steps: int, flush=None) -> float:
+    """Median CUDA-event time of fn() on the current stream; `flush` (a buffer larger than L2) is rewritten in between."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def run_lm(args) -> None:
+    import torch
+    from dia_tts_prune_b200 import engine as DE
+    from dia_tts_prune_b200 import synthetic as SY
+    from dia_tts_prune_b200.lm_config import PubopelConfig
+    from dia_tts_prune_b200.lm_engine import launch_count, linear
+    from dia_tts_prune_b200.lm_model import CausalLM
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        hbm, tf, src = float(pk["hbm_gbs"]), float(pk["bf16_tflops"]), "measured"
+    except Exception:
+        hbm, tf, src = 6650.0, 1590.0, "fallback"
+    flush = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)             # > the 126 MB L2
+    W, K = max(args.warmup, 3), max(args.steps, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    out = {}
+    for name in (args.lm_sizes.split(",") if args.lm_sizes else LM_SIZES):
+        sz = LM_SIZES[name]
+        cfg = SY.pubopel_config(**sz)
+        weights = SY.pubopel_weights(cfg, WEIGHT_SEED, dev)
+        T, ctx = args.lm_prompt, args.lm_context
+        model = CausalLM(PubopelConfig.model_validate(cfg), weights, dtype="bfloat16", device=dev,
+                         max_tokens=max(T, 8 * (ctx + 32 * (K + 2))) + 64, max_sequences=8, page_size=64, max_rows=1024)
+        del weights
+        D, H, G, d = sz["width"], sz["heads"], sz["kv_heads"], sz["dim"]
+        nq, nk, F, Sf, E, top, V, L = H * d, G * d, sz["expert_ff"], sz["shared_ff"], sz["experts"], sz["top"], sz["vocab"], sz["layers"]
+        win, keep = sz["window"], sz["keep_first"]
+        g = torch.Generator().manual_seed(7)
+        toks = torch.randint(0, V, (T,), generator=g).tolist()
+        res = {"config": sz}
+
+        # -- prefill: one prompt of T tokens through the step function (portions of 1024 rows), logits of the last token
+        def prefill():
+            model.run_step([{"id": "p", "tokens": toks, "want": [T - 1]}], ["p"])
+        ms = _event_ms(prefill, W, K, flush)
+        seen = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(T))
+        flops = L * (2.0 * T * D * (nq + nk) + 2.0 * T * nq * D + 2.0 * T * D * E + top * 6.0 * T * D * F + 6.0 * T * D * Sf
+                     + 4.0 * d * H * seen) + 2.0 * D * V
+        res["prefill"] = {"tokens": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "model_tflops": flops / ms / 1e9,
+                          "frac_of_bf16_peak": flops / ms / 1e9 / tf}
+
+        # -- decode: B sequences of `ctx` tokens each, one token per sequence per step, teacher-forced, device-timed
+        for B in (1, 8):
+            for b in range(B):
+                model.run_step([{"id": f"d{b}", "tokens": toks[:ctx], "want": []}])
+            n_dec = 32
+            def decode():
+                for t in range(n_dec):
+                    model.run_step([{"id": f"d{b}", "tokens": [toks[(ctx + t) % T]], "want": [0]} for b in range(B)])
+            ms = _event_ms(decode, 1, K) / n_dec
+            for b in range(B):
+                model.state.close(f"d{b}")
+            entry = {"context": ctx, "ms_per_step": ms, "tokens_per_s": B / ms * 1e3}
+            if B == 1:      # bytes one step must read: this token's share of the weights (bf16) and its visible keys + values (fp32)
+                n_keys = min(ctx, win) + min(keep, max(0, ctx - win))
+                byt = L * (2.0 * (D * (nq + nk) + nq * D + E * D + top * 3 * D * F + 3 * D * Sf) + 8.0 * n_keys * G * d) + 2.0 * D * V
+                entry.update(algorithmic_bytes=byt, gb_per_s=byt / ms / 1e6, frac_of_hbm_peak=byt / ms / 1e6 / hbm)
+            res[f"decode_b{B}"] = entry
+
+        # -- end to end: generate() through the scheduler, prompts from host lists, sampled ids back on the host
+        prompts = [toks[:256] for _ in range(8)]
+        model.generate(prompts[:1], max_new_tokens=4)
+        t0 = time.perf_counter()
+        outs = model.generate(prompts, max_new_tokens=64)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        res["generate_e2e"] = {"requests": 8, "prompt": 256, "new_tokens": 64, "wall_s": wall,
+                               "new_tokens_per_s": sum(len(o) for o in outs) / wall}
+
+        # -- kernels alone, beside Dia's at equal size
+        M = 1024
+        kern = {}
+        for label, (N_, K_) in {"qk_proj": (nq + nk, D), "o_proj": (D, nq), "shared_gate_up": (2 * Sf, D)}.items():
+            a = torch.randn(M, K_, device=dev)
+            w = (torch.randn(N_, K_, device=dev) * K_ ** -0.5).to(torch.bfloat16)
+            ms_lm = _event_ms(lambda: linear(a, w, tensor_cores=True), W, K, flush)
+            kern[label] = {"M": M, "N": N_, "K": K_, "pubopel_ms": ms_lm, "pubopel_frac_of_bf16_peak": 2.0 * M * N_ * K_ / ms_lm / 1e9 / tf}
+            if DE.dense_supported(M, N_, K_):
+                ms_dia = _event_ms(lambda: DE.dense_forward(a, w), W, K, flush)
+                kern[label].update(dia_ms=ms_dia, dia_frac_of_bf16_peak=2.0 * M * N_ * K_ / ms_dia / 1e9 / tf)
+        # attention: T rows of one sequence, full causal (no window) so that both kernels do the same work
+        eng = model.engine
+        full = CausalLM(PubopelConfig.model_validate(SY.pubopel_config(**{**sz, "layers": 1, "window": None, "vocab": 256,
+                                                                           "experts": 1, "top": 1, "expert_ff": 8, "shared_ff": None})),
+                        SY.pubopel_weights(SY.pubopel_config(**{**sz, "layers": 1, "window": None, "vocab": 256, "experts": 1,
+                                                                "top": 1, "expert_ff": 8, "shared_ff": None}), 3, dev),
+                        dtype="float32", device=dev, max_tokens=T + 64, max_sequences=2, page_size=64, max_rows=1024)
+        qk = torch.randn(T, nq + nk, device=dev)
+        def lm_attn():
+            seq = full.state.open("a")
+            for r0 in range(0, T, 1024):
+                n = min(1024, T - r0)
+                full.state.reserve(seq, n)
+                full.engine.op_attention(0, qk[r0:r0 + n], [(seq, n, r0)])
+                full.state.advance(seq, n)
+            full.state.close("a")
+        ms_lm = _event_ms(lm_attn, 2, K, flush)
+        a_flops = 4.0 * d * H * T * (T + 1) / 2
+        kern["attention_causal"] = {"T": T, "heads": H, "kv_heads": G, "dim": d, "pubopel_ms": ms_lm,
+                                    "pubopel_tflops_fp32": a_flops / ms_lm / 1e9}
+        if d == 128:
+            q4 = torch.randn(1, T, H, d, device=dev)
+            kc, vc = torch.randn(1, G, T, d, device=dev), torch.randn(1, G, T, d, device=dev)
+            ms_dia = _event_ms(lambda: DE.attention_rows(q4, kc, vc, T, 0, [T]), 2, K, flush)
+            kern["attention_causal"].update(dia_ms=ms_dia, dia_tflops_fp32=a_flops / ms_dia / 1e9)
+        res["kernels"] = kern
+        out[name] = res
+        model.engine.close(); full.engine.close()
+        del model, full
+        torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "lm_layer_throughput", "impl": "ours", "n_gpus": 1, "steps": K, "warmup": W, "dtype": "bf16",
+                      "data": "synthetic (random weights, random token ids)", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+                      "timing": "CUDA events, median; a 160 MB buffer is rewritten between timed iterations (L2 flush)",
+                      "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -500,7 +656,16 @@ def main():
     ap.add_argument("--per-launch", type=int, default=8, help="utterances decoded together in one kernel launch (1..8)")
     ap.add_argument("--batch-utterances", type=int, default=64,
                     help="headline mode: also run configs[4] with this many transcripts (0 = skip) and print it as `batch`")
+    ap.add_argument("--lm", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the decoder-only language-model path "
+                         "(Pubopel, random weights) at layer sizes of a real model, beside Dia's kernels at equal size")
+    ap.add_argument("--lm-sizes", default="", help="--lm: comma-separated subset of " + ",".join(LM_SIZES))
+    ap.add_argument("--lm-prompt", type=int, default=4096, help="--lm: prompt tokens of the prefill measurement")
+    ap.add_argument("--lm-context", type=int, default=1024, help="--lm: tokens each sequence holds before the decode measurement")
     args = ap.parse_args()
+    if args.lm:
+        run_lm(args)
+        return
     if args.impl == "reference":
         run_reference(args)
         return

@@ -82,6 +82,7 @@ struct lm_b200_engine {
     int *sel_e, *slot_of, *a_row, *a_expert, *n_slots;
     // bf16 operands of the tensor-core products (bfloat16 precision only)
     void *hb, *attb, *packb, *midb, *smidb, *hwb;
+    float* split_ws;                             // partial results of the key splits of a few rows' attention
 };
 
 namespace {
@@ -166,7 +167,7 @@ int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void*
                                  v.rm, M, st));
     const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
     const bool tc_o = tensor_path(e, M, D, nq);
-    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, tc_o ? e->attb : nullptr, M, st));
+    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, tc_o ? e->attb : nullptr, e->split_ws, M, st));
     if (tc_o) {
         if (fuse_x) {
             const dia::GemmEpilogue ep{fuse_x, l.norm_mix_out.w, l.norm_mix_out.b, l.norm_mix_out.alpha};
@@ -290,6 +291,10 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
                  o_slot_of = take(R * top * 4), o_a_row = take(slots * 4), o_a_scale = take(slots * 4),
                  o_a_expert = take(slots * 4), o_n_slots = take(4), o_gu = take(slots * 2 * F * 4), o_mid = take(slots * F * 4),
                  o_parts = take(slots * D * 4), o_sgu = take(R * 2 * Sf * 4), o_smid = take(R * Sf * 4), o_hw = take(R * D * 4);
+    size_t split = 0;
+    for (const lm_b200_layer& l : e->layers)
+        split = std::max(split, (size_t)lm::kAttnRowsKernelMax * l.heads * lm::kAttnSplitsMax * (l.dim + 2) * 4);
+    const size_t o_split = take(split);
     const bool tcb = m.precision == LM_B200_PRECISION_BF16;
     const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
                  o_midb = take(tcb ? slots * F * 2 : 0), o_smidb = take(tcb ? R * Sf * 2 : 0), o_hwb = take(tcb ? R * D * 2 : 0);
@@ -308,6 +313,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->smid = (float*)(b + o_smid); e->hw = (float*)(b + o_hw);
     e->hb = b + o_hb; e->attb = b + o_attb; e->packb = b + o_packb; e->midb = b + o_midb; e->smidb = b + o_smidb;
     e->hwb = b + o_hwb;
+    e->split_ws = (float*)(b + o_split);
     *out = e;
     return LM_B200_OK;
 }
@@ -380,6 +386,23 @@ int lm_b200_op_mixer(lm_b200_engine* e, int layer, const float* h, const int32_t
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
     return mixer(e, e->layers[layer], h, nullptr, view(step, M, n_seq), M, y, nullptr, S(stream));
+}
+
+int lm_b200_op_attention(lm_b200_engine* e, int layer, float* qk, const int32_t* step, int M, int n_seq, float* out,
+                         void* stream) {
+    if (!e || layer < 0 || layer >= e->m.n_layer || !qk || !step || !out || M <= 0 || M > e->m.max_rows || n_seq <= 0)
+        return LM_B200_EINVAL;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    const lm_b200_layer& l = e->layers[layer];
+    const StepView v = view(step, M, n_seq);
+    const int nq = l.heads * l.dim, nk = l.kv_heads * l.dim;
+    const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
+    LCK(lm::launch_qk_norm_cache(qk, nq, nk, l.q_norm, l.k_norm, e->m.eps, l.k_pages, l.v_pages, pm, l.kv_heads, l.dim, v.rm, M,
+                                 S(stream)));
+    const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
+    LCK(lm::launch_sink_attention(qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, out, nullptr, e->split_ws, M, S(stream)));
+    return LM_B200_OK;
 }
 
 int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y, void* stream) {

@@ -8,8 +8,10 @@ namespace lm {
 
 constexpr int kMaxTaps = 16;          // taps of the causal tap mix (the tail keeps taps - 1 rows per sequence)
 constexpr int kRowsKernelMax = 8;     // up to this many rows a linear layer runs one warp per output element
+constexpr int kRowsKernelMaxOut = 64; // ... and a linear layer of up to this many outputs at any number of rows
 constexpr int kTileRows = 64;         // row tile of the tiled linear kernel = padding of an expert group on that kernel
-constexpr int kAttnRowsKernelMax = 8; // up to this many rows attention runs one CTA per (row, head)
+constexpr int kAttnRowsKernelMax = 8; // up to this many rows attention splits every row's keys over CTAs
+constexpr int kAttnSplitsMax = 32;    // most key splits of a row (sizes the partial-result workspace)
 
 struct NormW { const float* w; const float* b; float alpha; };                  // DynamicTanh: tanh(alpha x) w + b
 struct RowMeta { const int* slot; const int* pos; const int* start; };          // per row of the step
@@ -44,7 +46,8 @@ cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, con
                                  float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
                                  cudaStream_t st);
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
-                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, int M, cudaStream_t st);
+                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws, int M,
+                                  cudaStream_t st);
 cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st);
 cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign, int top, int E, int pad, const GroupMap& gm,
                              int* slot_of, int max_slots, cudaStream_t st);

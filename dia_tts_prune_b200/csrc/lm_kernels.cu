@@ -23,8 +23,9 @@
 //   down_combine_rows_kernel   down products of a row's experts and the shared expert, their sum, norm, residual add
 //   router_rows_kernel         router logits, top experts, scores and the assignment maps of a handful of rows
 //   qk_norm_cache_kernel       whole-projection RMS norm of q and k, raw k and normed k scattered into the paged cache
-//   sink_attention_kernel      softmax attention over the pages with per-head temperature, tanh cap, linear distance
-//                              bias, a window that keeps the first tokens, and a value-less sink term in the denominator
+//   sink_attention_split_kernel / _combine_kernel   softmax attention over the pages for a handful of rows, split over
+//                              the keys: per-head temperature, tanh cap, linear distance bias, a window that keeps the
+//                              first tokens, and a value-less sink term in the denominator
 //   sink_attention_tile_kernel the same for prompt portions: 64 queries share the key / value tiles (flash-style)
 //   pack_rows_bf16_kernel      the expert-grouped, score-scaled bf16 operand of the tensor-core products
 //   router_topk_kernel         sigmoid scores and the `top` best experts of every row
@@ -32,6 +33,8 @@
 //   silu_mul_kernel            silu(gate) * up on [gate | up] rows
 //   residual_dyt_kernel        x += DynamicTanh(y [+ the row's expert outputs])
 //   dyt_gather_kernel          DynamicTanh of selected rows (the rows whose logits are wanted)
+#include <algorithm>
+
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
@@ -287,19 +290,30 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const 
     const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(arow) & 15) == 0);
     if (vec) {
-        for (int k = lane * 8; k < K; k += 256) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k);
-            const float4 x0 = *reinterpret_cast<const float4*>(arow + k);
-            const float4 x1 = *reinterpret_cast<const float4*>(arow + k + 4);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&wv);
-            acc = fmaf(x0.x * sc, __low2float(p[0]), acc);
-            acc = fmaf(x0.y * sc, __high2float(p[0]), acc);
-            acc = fmaf(x0.z * sc, __low2float(p[1]), acc);
-            acc = fmaf(x0.w * sc, __high2float(p[1]), acc);
-            acc = fmaf(x1.x * sc, __low2float(p[2]), acc);
-            acc = fmaf(x1.y * sc, __high2float(p[2]), acc);
-            acc = fmaf(x1.z * sc, __low2float(p[3]), acc);
-            acc = fmaf(x1.w * sc, __high2float(p[3]), acc);
+        // four 16-byte weight loads per lane in flight before their products (the sum keeps its order: k ascending)
+        for (int k0 = lane * 8; k0 < K; k0 += 1024) {
+            uint4 wv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int k = k0 + 256 * u;
+                wv[u] = k < K ? *reinterpret_cast<const uint4*>(wrow + k) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int k = k0 + 256 * u;
+                if (k >= K) break;
+                const float4 x0 = *reinterpret_cast<const float4*>(arow + k);
+                const float4 x1 = *reinterpret_cast<const float4*>(arow + k + 4);
+                const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+                acc = fmaf(x0.x * sc, __low2float(p[0]), acc);
+                acc = fmaf(x0.y * sc, __high2float(p[0]), acc);
+                acc = fmaf(x0.z * sc, __low2float(p[1]), acc);
+                acc = fmaf(x0.w * sc, __high2float(p[1]), acc);
+                acc = fmaf(x1.x * sc, __low2float(p[2]), acc);
+                acc = fmaf(x1.y * sc, __high2float(p[2]), acc);
+                acc = fmaf(x1.z * sc, __low2float(p[3]), acc);
+                acc = fmaf(x1.w * sc, __high2float(p[3]), acc);
+            }
         }
     } else {
         for (int k = lane; k < K; k += 32) acc = fmaf(arow[k] * sc, bf(wrow[k]), acc);
@@ -444,102 +458,128 @@ __global__ void qk_norm_cache_kernel(float* __restrict__ qk, int nq, int nk, con
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One CTA per (row, query head).  Query position i sees key j <= i when i - j < window or j < keep_first (window <= 0:
-// every j <= i).  score = cap * tanh(q.k * scale * temp_h / cap) - slope_h * (i - j)  (cap <= 0: no cap).  The softmax
-// denominator also holds exp(sink_h) when a sink is given (no key, no value): the running maximum starts at the sink.
-constexpr int kAttnThreads = 128;
-constexpr int kAttnWarps = kAttnThreads / 32;
+// Attention of a few rows (decoding), split over the keys.  Query position i sees key j <= i when i - j < window or
+// j < keep_first (window <= 0: every j <= i).  score = cap * tanh(q.k * scale * temp_h / cap) - slope_h * (i - j)
+// (cap <= 0: no cap).  One CTA per (row, up to HG query heads of one key/value head, split of the visible keys): a warp
+// takes every fourth key of the split, reads its key and value rows once for all HG heads (lanes over the head size,
+// coalesced), and keeps a running (maximum, denominator, weighted value sum) per head; the CTA's warps are merged and
+// written as one partial per (row, head, split).  sink_attention_combine_kernel merges the splits in their fixed order
+// and adds the sink: exp(sink_h) joins the denominator only (no key, no value).
+constexpr int kSplitThreads = 128, kSplitWarps = kSplitThreads / 32;
 constexpr int kAttnMaxDimPerLane = 8;                         // head dim <= 256
 
-__global__ void __launch_bounds__(kAttnThreads)
-sink_attention_kernel(const float* __restrict__ qk, int q_stride, const float* __restrict__ kcache,
-                      const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
-                      int heads, int kv_heads, int dim, float scale, float cap, const float* __restrict__ temp,
-                      const float* __restrict__ slopes, const float* __restrict__ sink, int window, int keep_first,
-                      const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out,
-                      __nv_bfloat16* __restrict__ out_b) {
-    extern __shared__ __align__(16) float sm[];
-    float* qs = sm;                                           // [dim]
-    float* ps = qs + ((dim + 3) & ~3);                        // [kAttnThreads]
-    float* acc_s = ps + kAttnThreads;                         // [kAttnWarps][dim]
-    __shared__ float red[32];
-    const int r = blockIdx.x, h = blockIdx.y;
-    const int g = h / (heads / kv_heads);
+template <int HG>
+__global__ void __launch_bounds__(kSplitThreads)
+sink_attention_split_kernel(const float* __restrict__ qk, int q_stride, const float* __restrict__ kcache,
+                            const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
+                            int heads, int kv_heads, int dim, float scale, float cap, const float* __restrict__ temp,
+                            const float* __restrict__ slopes, int window, int keep_first, const int* __restrict__ row_slot,
+                            const int* __restrict__ row_pos, float* __restrict__ part) {
+    __shared__ float sm_m[kSplitWarps][HG], sm_l[kSplitWarps][HG];
+    __shared__ float sm_acc[kSplitWarps][HG][32 * kAttnMaxDimPerLane];
+    const int r = blockIdx.x, S = gridDim.z, sp = blockIdx.z;
+    const int group = heads / kv_heads, chunks = (group + HG - 1) / HG;
+    const int g = blockIdx.y / chunks, h0 = g * group + (blockIdx.y % chunks) * HG;
+    const int nh = min(HG, (g + 1) * group - h0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int i = row_pos[r];
     const int* pages = table + (size_t)row_slot[r] * max_pages;
-    for (int c = tid; c < dim; c += kAttnThreads) qs[c] = qk[(size_t)r * q_stride + (size_t)h * dim + c];
-    const float mult = scale * (temp ? temp[h] : 1.f);
-    const float slope = slopes ? slopes[h] : 0.f;
     const int lo = window > 0 ? max(0, i - window + 1) : 0;
     const int n_keep = window > 0 ? min(keep_first, lo) : 0;
     const int n_keys = n_keep + (i - lo + 1);
-    const bool vec = (dim % 4) == 0;
+    const int per = (n_keys + S - 1) / S;
+    const int k_begin = sp * per, k_end = min(n_keys, k_begin + per);
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
-    float m_run = sink ? sink[h] : -CUDART_INF_F;
-    float l_part = 0.f;                                       // this thread's share of the denominator
-    float acc[kAttnMaxDimPerLane];
+    float q[HG][kAttnMaxDimPerLane], acc[HG][kAttnMaxDimPerLane], m_run[HG], l_run[HG], mult[HG], slope[HG];
 #pragma unroll
-    for (int u = 0; u < kAttnMaxDimPerLane; ++u) acc[u] = 0.f;
-    __syncthreads();
-
-    for (int t0 = 0; t0 < n_keys; t0 += kAttnThreads) {
-        const int kk = t0 + tid;
-        float s = -CUDART_INF_F;
-        if (kk < n_keys) {
-            const int j = kk < n_keep ? kk : lo + (kk - n_keep);
-            const float* kp = kcache + (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim;
+    for (int hh = 0; hh < HG; ++hh) {
+        const int h = h0 + min(hh, nh - 1);
+        mult[hh] = scale * (temp ? temp[h] : 1.f);
+        slope[hh] = slopes ? slopes[h] : 0.f;
+        m_run[hh] = -CUDART_INF_F; l_run[hh] = 0.f;
+#pragma unroll
+        for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
+            const int c = lane + 32 * u;
+            q[hh][u] = c < dim ? qk[(size_t)r * q_stride + (size_t)h * dim + c] : 0.f;
+            acc[hh][u] = 0.f;
+        }
+    }
+    for (int kk = k_begin + warp; kk < k_end; kk += kSplitWarps) {
+        const int j = kk < n_keep ? kk : lo + (kk - n_keep);
+        const size_t at = (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim;
+        float kv[kAttnMaxDimPerLane], vv[kAttnMaxDimPerLane];
+#pragma unroll
+        for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
+            const int c = lane + 32 * u;
+            kv[u] = c < dim ? kcache[at + c] : 0.f;
+            vv[u] = c < dim ? vcache[at + c] : 0.f;
+        }
+        const float dist = (float)(i - j);
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
             float d = 0.f;
-            if (vec) {
-                for (int c = 0; c < dim; c += 4) {
-                    const float4 kv = *reinterpret_cast<const float4*>(kp + c);
-                    const float4 qv = *reinterpret_cast<const float4*>(qs + c);
-                    d = fmaf(qv.x, kv.x, d); d = fmaf(qv.y, kv.y, d); d = fmaf(qv.z, kv.z, d); d = fmaf(qv.w, kv.w, d);
-                }
-            } else {
-                for (int c = 0; c < dim; ++c) d = fmaf(qs[c], kp[c], d);
-            }
-            s = d * mult;
-            if (cap > 0.f) s = cap * tanhf(s / cap);
-            s -= slope * (float)(i - j);
-        }
-        const float m_new = fmaxf(m_run, block_max(s, red));
-        const float corr = (m_run == -CUDART_INF_F) ? 0.f : expf(m_run - m_new);
-        const float p = (kk < n_keys) ? expf(s - m_new) : 0.f;
-        l_part = l_part * corr + p;
 #pragma unroll
-        for (int u = 0; u < kAttnMaxDimPerLane; ++u) acc[u] *= corr;
-        m_run = m_new;
-        __syncthreads();                                      // the previous tile's ps is consumed
-        ps[tid] = p;
-        __syncthreads();
-        const int n_tile = min(kAttnThreads, n_keys - t0);
-        for (int e = warp; e < n_tile; e += kAttnWarps) {
-            const int k2 = t0 + e;
-            const int j = k2 < n_keep ? k2 : lo + (k2 - n_keep);
-            const float* vp = vcache + (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim;
-            const float pe = ps[e];
+            for (int u = 0; u < kAttnMaxDimPerLane; ++u) d = fmaf(q[hh][u], kv[u], d);
+            float sc = warp_sum(d) * mult[hh];
+            if (cap > 0.f) sc = cap * tanhf(sc * inv_cap);
+            sc -= slope[hh] * dist;
+            const float m_new = fmaxf(m_run[hh], sc);
+            const float corr = expf(m_run[hh] - m_new);       // exp(-inf) = 0 at the first key
+            const float p = expf(sc - m_new);
+            l_run[hh] = l_run[hh] * corr + p;
+            m_run[hh] = m_new;
 #pragma unroll
-            for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
-                const int c = lane + 32 * u;
-                if (c < dim) acc[u] = fmaf(pe, vp[c], acc[u]);
-            }
+            for (int u = 0; u < kAttnMaxDimPerLane; ++u) acc[hh][u] = fmaf(p, vv[u], acc[hh][u] * corr);
         }
     }
-    float l = block_sum(l_part, red);
-    if (sink) l += expf(sink[h] - m_run);                     // the sink's own term (exp(0) while it is the maximum)
 #pragma unroll
-    for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
-        const int c = lane + 32 * u;
-        if (c < dim) acc_s[warp * dim + c] = acc[u];
+    for (int hh = 0; hh < HG; ++hh) {
+        if (lane == 0) { sm_m[warp][hh] = m_run[hh]; sm_l[warp][hh] = l_run[hh]; }
+#pragma unroll
+        for (int u = 0; u < kAttnMaxDimPerLane; ++u) sm_acc[warp][hh][lane + 32 * u] = acc[hh][u];
     }
     __syncthreads();
-    for (int c = tid; c < dim; c += kAttnThreads) {
-        float o = 0.f;
+    // merge the warps (fixed order); part[((r * heads + h) * S + sp)] = {maximum, denominator, sums[dim]}
+    for (int hh = 0; hh < nh; ++hh) {
+        float m = -CUDART_INF_F;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) o += acc_s[w * dim + c];
-        out[((size_t)r * heads + h) * dim + c] = o / l;
-        if (out_b) out_b[((size_t)r * heads + h) * dim + c] = __float2bfloat16_rn(o / l);
+        for (int w = 0; w < kSplitWarps; ++w) m = fmaxf(m, sm_m[w][hh]);
+        float* dst = part + ((size_t)(r * heads + h0 + hh) * S + sp) * (dim + 2);
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kSplitWarps; ++w) l += sm_m[w][hh] == -CUDART_INF_F ? 0.f : sm_l[w][hh] * expf(sm_m[w][hh] - m);
+        if (tid == 0) { dst[0] = m; dst[1] = l; }
+        for (int c = tid; c < dim; c += kSplitThreads) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSplitWarps; ++w) o += sm_m[w][hh] == -CUDART_INF_F ? 0.f : sm_acc[w][hh][c] * expf(sm_m[w][hh] - m);
+            dst[2 + c] = o;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128)
+sink_attention_combine_kernel(const float* __restrict__ part, int S, int heads, int dim, const float* __restrict__ sink,
+                              float* __restrict__ out, __nv_bfloat16* __restrict__ out_b) {
+    const int r = blockIdx.x, h = blockIdx.y;
+    const float* src = part + (size_t)(r * heads + h) * S * (dim + 2);
+    float m = sink ? sink[h] : -CUDART_INF_F;
+    for (int s = 0; s < S; ++s) m = fmaxf(m, src[(size_t)s * (dim + 2)]);
+    float l = sink ? expf(sink[h] - m) : 0.f;
+    for (int s = 0; s < S; ++s) {
+        const float ms = src[(size_t)s * (dim + 2)];
+        if (ms != -CUDART_INF_F) l += src[(size_t)s * (dim + 2) + 1] * expf(ms - m);
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < S; ++s) {
+            const float ms = src[(size_t)s * (dim + 2)];
+            if (ms != -CUDART_INF_F) o += src[(size_t)s * (dim + 2) + 2 + c] * expf(ms - m);
+        }
+        out[((size_t)r * heads + h) * dim + c] = o * inv;
+        if (out_b) out_b[((size_t)r * heads + h) * dim + c] = __float2bfloat16_rn(o * inv);
     }
 }
 
@@ -571,13 +611,14 @@ sink_attention_tile_kernel(const float* __restrict__ qk, int q_stride, const flo
     int* s_pos = s_slot + kTQ;                                // [64]
 
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int r0 = blockIdx.x * kTQ, h = blockIdx.y;
+    const int r0 = (gridDim.x - 1 - blockIdx.x) * kTQ, h = blockIdx.y;    // later rows see more keys: they start first
     const int n_rows = min(kTQ, M - r0);
     const int g = h / (heads / kv_heads);
     const bool vec = (dim % 4) == 0 && (q_stride % 4) == 0;
     const float mult = scale * (temp ? temp[h] : 1.f);
     const float slope = slopes ? slopes[h] : 0.f;
     const float sink_h = sink ? sink[h] : -CUDART_INF_F;
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
     if (tid < kTQ) {
         s_slot[tid] = tid < n_rows ? row_slot[r0 + tid] : -1;
@@ -674,7 +715,7 @@ sink_attention_tile_kernel(const float* __restrict__ qk, int q_stride, const flo
                         const int key = j0 + tx + 16 * j;
                         const bool ok = live && key < k_end && key <= qi && (window <= 0 || qi - key < window || key < keep_first);
                         float v = sc[i][j] * mult;
-                        if (cap > 0.f) v = cap * tanhf(v / cap);
+                        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
                         v -= slope * (float)(qi - key);
                         sc[i][j] = ok ? v : -CUDART_INF_F;
                         mx = fmaxf(mx, sc[i][j]);
@@ -927,7 +968,9 @@ cudaError_t launch_linear(const float* A, int lda, const void* W, long long w_ex
     const int* a_expert = gm ? gm->a_expert : nullptr;
     const int* n_slots = gm ? gm->n_slots : nullptr;
     const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
-    if (M <= kRowsKernelMax)
+    // a few rows, or a few outputs (router logits: the same kernel for every step length, so that the choice of experts
+    // does not depend on how a prompt was cut)
+    if (M <= kRowsKernelMax || (N <= kRowsKernelMaxOut && M <= 65535))
         linear_rows_kernel<<<dim3((N + 7) / 8, M), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N, K, a_row, a_scale,
                                                                  a_expert, n_slots, nullptr, nullptr, nullptr, 0.f);
     else
@@ -1003,9 +1046,30 @@ static cudaError_t launch_attention_tiles(const float* qk, int q_stride, const f
     return cudaGetLastError();
 }
 
-// a step of a few rows (decoding) runs one CTA per (row, head); longer steps the tiled kernel
+template <int HG>
+static cudaError_t launch_attention_splits(const float* qk, int q_stride, const float* kcache, const float* vcache,
+                                           const PageMap& pm, const AttnShape& a, const RowMeta& rm, float* out,
+                                           __nv_bfloat16* out_b, int M, float* split_ws, cudaStream_t st) {
+    const int group = a.heads / a.kv_heads, chunks = (group + HG - 1) / HG;
+    // enough CTAs for two per SM, at least 16 keys per split where the window bounds the keys
+    const long long max_keys = a.window > 0 ? (long long)a.window + a.keep_first : (long long)pm.max_pages * pm.page_size;
+    const int others = M * a.kv_heads * chunks;
+    int S = (2 * 148 + others - 1) / others;
+    S = (int)std::max<long long>(1, std::min<long long>(std::min(S, kAttnSplitsMax), (max_keys + 15) / 16));
+    sink_attention_split_kernel<HG><<<dim3(M, a.kv_heads * chunks, S), kSplitThreads, 0, st>>>(
+        qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
+        a.temp, a.slopes, a.window, a.keep_first, rm.slot, rm.pos, split_ws);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    sink_attention_combine_kernel<<<dim3(M, a.heads), 128, 0, st>>>(split_ws, S, a.heads, a.dim, a.sink, out, out_b);
+    return cudaGetLastError();
+}
+
+// a step of a few rows (decoding) splits every row's keys over CTAs; longer steps run the tiled kernel.
+// split_ws: kRowsKernelMax * heads * kAttnSplitsMax * (dim + 2) floats
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
-                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, int M, cudaStream_t st) {
+                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws, int M,
+                                  cudaStream_t st) {
     if (a.dim > 32 * kAttnMaxDimPerLane || a.heads % a.kv_heads) return cudaErrorNotSupported;
     __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out_bf16);
     if (M > kAttnRowsKernelMax) {
@@ -1016,11 +1080,10 @@ cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kc
             default: return launch_attention_tiles<4>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, st);
         }
     }
-    const size_t smem = (size_t)(((a.dim + 3) & ~3) + kAttnThreads + kAttnWarps * a.dim) * sizeof(float);
-    sink_attention_kernel<<<dim3(M, a.heads), kAttnThreads, smem, st>>>(
-        qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
-        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, out, ob);
-    return cudaGetLastError();
+    const int group = a.heads / a.kv_heads;
+    if (group >= 4) return launch_attention_splits<4>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, st);
+    if (group >= 2) return launch_attention_splits<2>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, st);
+    return launch_attention_splits<1>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, st);
 }
 
 cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st) {

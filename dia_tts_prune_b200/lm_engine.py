@@ -168,6 +168,18 @@ class LMEngine:
                                                 _stream(self.device)), "op_mixer")
         return y
 
+    def op_attention(self, layer: int, qk: torch.Tensor, parts) -> torch.Tensor:
+        """Attention of ``layer`` alone on projected rows ``qk [M, (heads + kv_heads) * dim]`` (queries, then keys), which
+        are appended to the pages of their sequences; ``parts``: (sequence, rows, first position) like ``op_mixer``."""
+        buf, M, S, _ = self._pack([(s, [0] * n, p0, []) for s, n, p0 in parts])
+        self.state.sync_table()
+        a = self.layers[layer].mixer
+        qk = qk.to(device=self.device, dtype=torch.float32).contiguous().clone()
+        out = torch.empty((M, a.heads * a.dim), dtype=torch.float32, device=self.device)
+        _lm_lib.check(self.lib.lm_b200_op_attention(self._h, layer, qk.data_ptr(), buf.data_ptr(), M, S, out.data_ptr(),
+                                                    _stream(self.device)), "op_attention")
+        return out
+
     def op_ff(self, layer: int, h: torch.Tensor) -> torch.Tensor:
         h = h.to(device=self.device, dtype=torch.float32).contiguous()
         y = torch.empty_like(h)

@@ -91,3 +91,57 @@ def synthetic_transcript(i: int, min_bytes: int = 60, max_bytes: int = 200) -> s
 
 DEFAULT_TRANSCRIPT = ("[S1] Dia is an open weights text to dialogue model. "
                       "[S2] You get full control over scripts and voices. [S1]")
+
+
+# ---- decoder-only language models: made-up configurations and random weights (benchmarks, smoke runs) ----------------
+def pubopel_config(width: int, layers: int, heads: int, kv_heads: int, dim: int, experts: int, top: int, expert_ff: int,
+                   shared_ff: int | None, vocab: int, window: int | None = None, keep_first: int = 0, taps: int = 4,
+                   softcap: float | None = 30.0) -> dict:
+    """A Pubopel ``config.json`` as a dictionary: ``layers`` equal layers of the given sizes."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": softcap,
+             "mask": {"size": window, "keep_first": keep_first} if window else None}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": shared_ff} if shared_ff else None}
+    return {"architecture": "Pubopel", "vocab": vocab, "width": width, "canon": {"taps": taps}, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": dict(mlp)} for _ in range(layers)]}
+
+
+def pubopel_weights(cfg: dict, seed: int = 1234, device="cpu") -> dict:
+    """Random bfloat16 tensors under the checkpoint's names: matrices ~ N(0, 1 / fan_in), norms near the identity."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, V = cfg["width"], cfg["vocab"]
+
+    def mat(n, k):
+        return (torch.randn((n, k), generator=g, device=device) * k ** -0.5).to(torch.bfloat16)
+
+    def vec(n, mean, spread):
+        return (mean + spread * torch.randn((n,), generator=g, device=device)).to(torch.bfloat16)
+
+    w = {"embed": (torch.randn((V, D), generator=g, device=device)).to(torch.bfloat16), "head": mat(V, D)}
+
+    def norm(name):
+        w[name], w[name + ".b"] = vec(D, 1.0, 0.05), vec(D, 0.0, 0.02)
+        w[name + ".alpha"] = torch.tensor(0.7, dtype=torch.bfloat16, device=device)
+
+    norm("final.norm")
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lc["mixer"]
+        nq, nk = m["heads"] * m["dim"], m["kv_heads"] * m["dim"]
+        norm(p + "norm1"); norm(p + "norm1b")
+        w[p + "canon1"] = (0.2 * torch.randn((D, cfg["canon"]["taps"]), generator=g, device=device)).to(torch.bfloat16)
+        w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.o"] = mat(nq, D), mat(nk, D), mat(D, nq)
+        w[p + "mix.q.norm"], w[p + "mix.k.norm"] = vec(nq, 1.0, 0.05), vec(nk, 1.0, 0.05)
+        w[p + "mix.temp"], w[p + "mix.sink"] = vec(m["heads"], 1.0, 0.1), vec(m["heads"], 0.0, 0.5)
+        if lc.get("mlp"):
+            f = lc["mlp"]
+            norm(p + "norm2"); norm(p + "norm2b")
+            w[p + "canon2"] = (0.2 * torch.randn((D, cfg["canon"]["taps"]), generator=g, device=device)).to(torch.bfloat16)
+            w[p + "mlp.router"] = mat(f["router"]["experts"], D)
+            for e in range(f["router"]["experts"]):
+                w[p + f"mlp.e{e}.gate"], w[p + f"mlp.e{e}.up"] = mat(f["expert"]["ff"], D), mat(f["expert"]["ff"], D)
+                w[p + f"mlp.e{e}.down"] = mat(D, f["expert"]["ff"])
+            if f.get("shared"):
+                sf = f["shared"]["ff"]
+                w[p + "mlp.shared.gate"], w[p + "mlp.shared.up"], w[p + "mlp.shared.down"] = mat(sf, D), mat(sf, D), mat(D, sf)
+    return w

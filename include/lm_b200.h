@@ -98,6 +98,10 @@ int lm_b200_op_norm_tapmix(lm_b200_engine *e, int layer, int sub, const float *x
 /* y = mixer(h): projections, norms, page append, attention, output projection */
 int lm_b200_op_mixer(lm_b200_engine *e, int layer, const float *h, const int32_t *step, int M, int n_seq, float *y,
                      void *stream);
+/* attention alone on projected rows qk [M][(heads + kv_heads) * dim] (query part, then key part): the whole-projection
+ * norms (q in place), the page append and the attention; out [M][heads * dim] */
+int lm_b200_op_attention(lm_b200_engine *e, int layer, float *qk, const int32_t *step, int M, int n_seq, float *out,
+                         void *stream);
 /* y = ff(h): router, expert groups, shared expert; the sum over a row's experts */
 int lm_b200_op_ff(lm_b200_engine *e, int layer, const float *h, int M, float *y, void *stream);
 /* Y[M][N] = A[M][K] . W[N][K]^T */
