@@ -35,7 +35,7 @@ class Layer(C.Structure):
 class Model(C.Structure):
     _fields_ = [("n_layer", _i), ("width", _i), ("vocab", _i), ("taps", _i), ("page_size", _i), ("max_pages", _i),
                 ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("precision", _i), ("embed", _vp), ("head", _vp),
-                ("final_norm", Norm), ("page_table", _vp)]
+                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("reserved", _i)]
 
 
 _ci = C.c_int

@@ -28,7 +28,9 @@
 #include <atomic>
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <new>
+#include <tuple>
 #include <vector>
 
 #include <cuda_runtime.h>
@@ -83,6 +85,12 @@ struct lm_b200_engine {
     // bf16 operands of the tensor-core products (bfloat16 precision only)
     void *hb, *attb, *packb, *midb, *smidb, *hwb;
     float* split_ws;                             // partial results of the key splits of a few rows' attention
+    // steps of a few rows are captured once per (rows, sequences, wanted) into a CUDA graph over these fixed buffers
+    int32_t* step_static = nullptr;
+    float* logits_static = nullptr;
+    cudaStream_t capture_stream = nullptr;       // captures run here (the caller's stream may be the legacy default stream)
+    struct StepGraph { cudaGraphExec_t exec; long long launches; };
+    std::map<std::tuple<int, int, int>, StepGraph> graphs;
 };
 
 namespace {
@@ -195,8 +203,8 @@ int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
     if (M <= lm::kRowsKernelMax) {
         const lm::GroupMap rows{e->a_row, e->a_scale, e->a_expert, e->n_slots};
         LCK(lm::launch_router_rows(h, D, l.w_router, E, top, M, e->z, rows, e->slot_of, st));
-        LCK(lm::launch_gated_rows(h, D, l.w_gate_up, 2LL * F * D, e->mid, M * top, F, D, &rows, st));
-        if (Sf > 0) LCK(lm::launch_gated_rows(h, D, l.ws_gate_up, 0, e->smid, M, Sf, D, nullptr, st));
+        LCK(lm::launch_gated_rows(h, D, l.w_gate_up, 2LL * F * D, e->mid, M * top, F, D, &rows, l.ws_gate_up, e->smid,
+                                  Sf > 0 ? M : 0, Sf, st));
         LCK(lm::launch_down_combine_rows(e->mid, F, l.w_down, e->a_expert, top, Sf > 0 ? e->smid : nullptr, Sf, l.ws_down, x, M, D,
                                          nrm, st));
         return LM_B200_OK;
@@ -295,6 +303,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     for (const lm_b200_layer& l : e->layers)
         split = std::max(split, (size_t)lm::kAttnRowsKernelMax * l.heads * lm::kAttnSplitsMax * (l.dim + 2) * 4);
     const size_t o_split = take(split);
+    const size_t o_step = take((size_t)(8 * lm::kRowsKernelMax) * 4), o_logits = take((size_t)lm::kRowsKernelMax * m.vocab * 4);
     const bool tcb = m.precision == LM_B200_PRECISION_BF16;
     const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
                  o_midb = take(tcb ? slots * F * 2 : 0), o_smidb = take(tcb ? R * Sf * 2 : 0), o_hwb = take(tcb ? R * D * 2 : 0);
@@ -314,6 +323,8 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->hb = b + o_hb; e->attb = b + o_attb; e->packb = b + o_packb; e->midb = b + o_midb; e->smidb = b + o_smidb;
     e->hwb = b + o_hwb;
     e->split_ws = (float*)(b + o_split);
+    e->step_static = (int32_t*)(b + o_step);
+    e->logits_static = (float*)(b + o_logits);
     *out = e;
     return LM_B200_OK;
 }
@@ -321,6 +332,8 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
 int lm_b200_engine_destroy(lm_b200_engine* e) {
     if (!e) return LM_B200_OK;
     Guard g(e->device);
+    for (auto& kv : e->graphs) cudaGraphExecDestroy(kv.second.exec);
+    if (e->capture_stream) cudaStreamDestroy(e->capture_stream);
     if (e->arena) cudaFree(e->arena);
     delete e;
     return LM_B200_OK;
@@ -328,14 +341,13 @@ int lm_b200_engine_destroy(lm_b200_engine* e) {
 
 size_t lm_b200_engine_workspace_bytes(const lm_b200_engine* e) { return e ? e->arena_bytes : 0; }
 
-int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_want, float* logits_out, float* layers_out,
-                    void* stream) {
-    if (!e || !step || M <= 0 || M > e->m.max_rows || n_seq <= 0 || n_seq > M || n_want < 0 || n_want > M ||
-        (n_want > 0 && !logits_out))
-        return LM_B200_EINVAL;
-    Guard g(e->device);
-    if (!g.ok) return LM_B200_ECUDA;
-    cudaStream_t st = S(stream);
+}  // extern "C"
+
+namespace {
+
+// the launch sequence of one step
+int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_want, float* logits_out, float* layers_out,
+             cudaStream_t st) {
     const StepView v = view(step, M, n_seq);
     const int D = e->m.width;
     LCK(lm::launch_embed(e->m.embed, v.token, e->x, M, e->m.vocab, D, st));
@@ -367,6 +379,60 @@ int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, in
             LCK(lm::launch_linear(e->hw, D, e->m.head, 0, logits_out, e->m.vocab, n_want, e->m.vocab, D, nullptr, st));
     }
     return LM_B200_OK;
+}
+
+// A step of a few rows is some forty short dependent launches: it is captured once per (rows, sequences, wanted) over
+// the engine's fixed step and logits buffers and replayed as one graph launch; the step description is copied in and
+// the logits out around it.
+int run_step_graph(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_want, float* logits_out, cudaStream_t st) {
+    const size_t n_ints = 4 * (size_t)M + 3 * (size_t)n_seq + (size_t)n_want;
+    if (cudaMemcpyAsync(e->step_static, step, n_ints * 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return cuda_fail(cudaGetLastError());
+    const auto key = std::make_tuple(M, n_seq, n_want);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        if (!e->capture_stream && cudaStreamCreateWithFlags(&e->capture_stream, cudaStreamNonBlocking) != cudaSuccess)
+            return cuda_fail(cudaGetLastError());
+        cudaStream_t cs = e->capture_stream;
+        if (cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed) != cudaSuccess) return cuda_fail(cudaGetLastError());
+        const long long before = g_launches.load();
+        const int rc = run_step(e, e->step_static, M, n_seq, n_want, e->logits_static, nullptr, cs);
+        const long long launches = g_launches.load() - before;
+        cudaGraph_t graph = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(cs, &graph);
+        if (rc != LM_B200_OK || ce != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc != LM_B200_OK ? rc : cuda_fail(ce != cudaSuccess ? ce : cudaErrorUnknown);
+        }
+        cudaGraphExec_t exec = nullptr;
+        const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) return cuda_fail(ie);
+        g_launches -= launches;                              // captured, not run: every replay counts them
+        it = e->graphs.emplace(key, lm_b200_engine::StepGraph{exec, launches}).first;
+    }
+    if (cudaGraphLaunch(it->second.exec, st) != cudaSuccess) return cuda_fail(cudaGetLastError());
+    g_launches += it->second.launches;
+    if (n_want > 0 && cudaMemcpyAsync(logits_out, e->logits_static, (size_t)n_want * e->m.vocab * 4, cudaMemcpyDeviceToDevice,
+                                      st) != cudaSuccess)
+        return cuda_fail(cudaGetLastError());
+    return LM_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lm_b200_forward(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_want, float* logits_out, float* layers_out,
+                    void* stream) {
+    if (!e || !step || M <= 0 || M > e->m.max_rows || n_seq <= 0 || n_seq > M || n_want < 0 || n_want > M ||
+        (n_want > 0 && !logits_out))
+        return LM_B200_EINVAL;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    if (e->m.step_graphs && M <= lm::kRowsKernelMax && !layers_out)
+        return run_step_graph(e, step, M, n_seq, n_want, logits_out, S(stream));
+    return run_step(e, step, M, n_seq, n_want, logits_out, layers_out, S(stream));
 }
 
 int lm_b200_op_norm_tapmix(lm_b200_engine* e, int layer, int sub, const float* x, const int32_t* step, int M, int n_seq,

@@ -36,8 +36,8 @@ cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* c
                                   const RowMeta& rm, int n_seq, float* out, int D, cudaStream_t st);
 cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
                                         cudaStream_t st);
-cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int M, int F, int K,
-                              const GroupMap* gm, cudaStream_t st);
+cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
+                              int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st);
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
                                      int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, cudaStream_t st);
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,

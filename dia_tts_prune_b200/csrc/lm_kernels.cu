@@ -344,24 +344,39 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     }
 }
 
-// mid[a][n] = silu(A_a . Wg_e[n]) * (A_a . Wu_e[n]),  W_e = [gate rows (F) | up rows (F)][K];  a: assignment slots (with
-// the maps) or rows
+// mid[a][n] = silu(A_a . Wg_e[n]) * (A_a . Wu_e[n]),  W_e = [gate rows (F) | up rows (F)][K].  blockIdx.y < n_assign: the
+// assignment slot a of the routed experts (row, expert and score from the maps); beyond: row blockIdx.y - n_assign through
+// the shared expert Ws (Sf hidden units) into smid.  One grid for both, so that the two weight streams overlap.
 __global__ void __launch_bounds__(256)
 gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
-                  float* __restrict__ mid, int M, int F, int K, const int* __restrict__ a_row, const float* __restrict__ a_scale,
-                  const int* __restrict__ a_expert) {
-    const int a = blockIdx.y;
-    const int src = a_row ? a_row[a] : a;
-    if (src < 0) return;
+                  float* __restrict__ mid, int n_assign, int F, int K, const int* __restrict__ a_row,
+                  const float* __restrict__ a_scale, const int* __restrict__ a_expert, const __nv_bfloat16* __restrict__ Ws,
+                  float* __restrict__ smid, int Sf) {
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (n >= F) return;
-    const float sc = a_scale ? a_scale[a] : 1.f;
-    const __nv_bfloat16* wg = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
+    int a = blockIdx.y, src, width;
+    float sc = 1.f;
+    const __nv_bfloat16* wg;
+    float* dst;
+    if (a < n_assign) {
+        src = a_row ? a_row[a] : a;
+        if (src < 0 || n >= F) return;
+        if (a_scale) sc = a_scale[a];
+        wg = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
+        width = F;
+        dst = mid + (size_t)a * F + n;
+    } else {
+        a -= n_assign;
+        if (n >= Sf) return;
+        src = a;
+        wg = Ws + (size_t)n * K;
+        width = Sf;
+        dst = smid + (size_t)a * Sf + n;
+    }
     const float* arow = A + (size_t)src * lda;
     const float g = warp_dot(arow, wg, K, lda, sc, lane);
-    const float u = warp_dot(arow, wg + (size_t)F * K, K, lda, sc, lane);
-    if (lane == 0) mid[(size_t)a * F + n] = (g / (1.0f + expf(-g))) * u;
+    const float u = warp_dot(arow, wg + (size_t)width * K, K, lda, sc, lane);
+    if (lane == 0) *dst = (g / (1.0f + expf(-g))) * u;
 }
 
 // v = smid[r] . Wsd[n] (with a shared expert) + sum_t mid[r * top + t] . Wd_{e(r, t)}[n];  x[r][n] += DynamicTanh(v), or
@@ -505,16 +520,26 @@ sink_attention_split_kernel(const float* __restrict__ qk, int q_stride, const fl
             acc[hh][u] = 0.f;
         }
     }
-    for (int kk = k_begin + warp; kk < k_end; kk += kSplitWarps) {
+    // the next key's rows are requested before the current key's arithmetic (a warp's keys are a dependent chain)
+    float kv[kAttnMaxDimPerLane], vv[kAttnMaxDimPerLane], kn[kAttnMaxDimPerLane], vn[kAttnMaxDimPerLane];
+    auto fetch = [&](int kk, float* kd, float* vd) -> int {
         const int j = kk < n_keep ? kk : lo + (kk - n_keep);
         const size_t at = (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim;
-        float kv[kAttnMaxDimPerLane], vv[kAttnMaxDimPerLane];
 #pragma unroll
         for (int u = 0; u < kAttnMaxDimPerLane; ++u) {
             const int c = lane + 32 * u;
-            kv[u] = c < dim ? kcache[at + c] : 0.f;
-            vv[u] = c < dim ? vcache[at + c] : 0.f;
+            kd[u] = c < dim ? kcache[at + c] : 0.f;
+            vd[u] = c < dim ? vcache[at + c] : 0.f;
         }
+        return j;
+    };
+    int j_next = 0;
+    if (k_begin + warp < k_end) j_next = fetch(k_begin + warp, kn, vn);
+    for (int kk = k_begin + warp; kk < k_end; kk += kSplitWarps) {
+        const int j = j_next;
+#pragma unroll
+        for (int u = 0; u < kAttnMaxDimPerLane; ++u) { kv[u] = kn[u]; vv[u] = vn[u]; }
+        if (kk + kSplitWarps < k_end) j_next = fetch(kk + kSplitWarps, kn, vn);
         const float dist = (float)(i - j);
 #pragma unroll
         for (int hh = 0; hh < HG; ++hh) {
@@ -564,20 +589,27 @@ sink_attention_combine_kernel(const float* __restrict__ part, int S, int heads, 
                               float* __restrict__ out, __nv_bfloat16* __restrict__ out_b) {
     const int r = blockIdx.x, h = blockIdx.y;
     const float* src = part + (size_t)(r * heads + h) * S * (dim + 2);
-    float m = sink ? sink[h] : -CUDART_INF_F;
-    for (int s = 0; s < S; ++s) m = fmaxf(m, src[(size_t)s * (dim + 2)]);
-    float l = sink ? expf(sink[h] - m) : 0.f;
-    for (int s = 0; s < S; ++s) {
-        const float ms = src[(size_t)s * (dim + 2)];
-        if (ms != -CUDART_INF_F) l += src[(size_t)s * (dim + 2) + 1] * expf(ms - m);
+    static_assert(kAttnSplitsMax <= 32, "one lane per split");
+    __shared__ float wgt[kAttnSplitsMax];                    // exp(m_s - m) per split, 0 for an empty one
+    __shared__ float inv_s;
+    if (threadIdx.x < 32) {                                   // one warp: S <= kAttnSplitsMax = 32 splits, one per lane
+        const int s = threadIdx.x;
+        const float ms = s < S ? src[(size_t)s * (dim + 2)] : -CUDART_INF_F;
+        const float ls = s < S ? src[(size_t)s * (dim + 2) + 1] : 0.f;
+        const float m = fmaxf(sink ? sink[h] : -CUDART_INF_F, warp_max(ms));
+        const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - m);
+        // the denominator in the fixed order of the splits
+        float l = sink ? expf(sink[h] - m) : 0.f;
+        for (int t = 0; t < S; ++t) l += __shfl_sync(0xffffffffu, ls * w, t);
+        if (s < S) wgt[s] = w;
+        if (s == 0) inv_s = l > 0.f ? 1.0f / l : 0.f;
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    __syncthreads();
+    const float inv = inv_s;
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
         float o = 0.f;
-        for (int s = 0; s < S; ++s) {
-            const float ms = src[(size_t)s * (dim + 2)];
-            if (ms != -CUDART_INF_F) o += src[(size_t)s * (dim + 2) + 2 + c] * expf(ms - m);
-        }
+#pragma unroll 8
+        for (int s = 0; s < S; ++s) o = fmaf(src[(size_t)s * (dim + 2) + 2 + c], wgt[s], o);
         out[((size_t)r * heads + h) * dim + c] = o * inv;
         if (out_b) out_b[((size_t)r * heads + h) * dim + c] = __float2bfloat16_rn(o * inv);
     }
@@ -994,11 +1026,12 @@ cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, 
     return cudaGetLastError();
 }
 
-cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int M, int F, int K,
-                              const GroupMap* gm, cudaStream_t st) {
-    gated_rows_kernel<<<dim3((F + 7) / 8, M), 256, 0, st>>>(A, lda, reinterpret_cast<const __nv_bfloat16*>(W), w_expert_stride, mid,
-                                                            M, F, K, gm ? gm->a_row : nullptr, gm ? gm->a_scale : nullptr,
-                                                            gm ? gm->a_expert : nullptr);
+cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
+                              int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st) {
+    const int widest = std::max(F, n_shared_rows > 0 ? Sf : 0);
+    gated_rows_kernel<<<dim3((widest + 7) / 8, n_assign + n_shared_rows), 256, 0, st>>>(
+        A, lda, reinterpret_cast<const __nv_bfloat16*>(W), w_expert_stride, mid, n_assign, F, K, gm ? gm->a_row : nullptr,
+        gm ? gm->a_scale : nullptr, gm ? gm->a_expert : nullptr, reinterpret_cast<const __nv_bfloat16*>(Ws), smid, Sf);
     return cudaGetLastError();
 }
 

@@ -27,7 +27,7 @@ def launch_count() -> int:
 class LMEngine:
     def __init__(self, layers: list[MixLayer], embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh, *,
                  width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024,
-                 precision: str = "bfloat16"):
+                 precision: str = "bfloat16", step_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("the language-model path needs a CUDA device (sm_100a); there is no CPU fallback")
         self.lib = _lm_lib.load()
@@ -52,6 +52,7 @@ class LMEngine:
         m.embed, m.head = self.embed.data_ptr(), self.head.data_ptr()
         final_norm.fill(m.final_norm)
         m.page_table = state.page_table.data_ptr()
+        m.step_graphs = 1 if step_graphs else 0
         recs = (_lm_lib.Layer * len(layers))()
         for i, layer in enumerate(layers):
             layer.fill(recs[i], state.k_pages[i], state.v_pages[i], state.tails[i][0], state.tails[i][1])
@@ -86,7 +87,9 @@ class LMEngine:
             s_count.append(n)
             want += [r0 + k for k in w]
         buf = torch.tensor(tok + slot + pos + start + s_slot + s_row0 + s_count + want, dtype=torch.int32)
-        return buf.pin_memory().to(self.device, non_blocking=True), len(tok), len(parts), len(want)
+        if buf.numel() > 4096:                                  # a long step: asynchronous copy from pinned memory
+            buf = buf.pin_memory()
+        return buf.to(self.device, non_blocking=True), len(tok), len(parts), len(want)
 
     def _forward(self, parts, logits_out: torch.Tensor | None, layers_out: torch.Tensor | None = None) -> None:
         buf, M, S, W = self._pack(parts)

@@ -145,7 +145,7 @@ class Scheduler:
 class CausalLM:
     def __init__(self, cfg: PubopelConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
                  max_tokens: int = 4096, max_sequences: int = 8, page_size: int = 16, max_rows: int = 1024,
-                 max_sequence_tokens: int | None = None):
+                 max_sequence_tokens: int | None = None, step_graphs: bool = True):
         if dtype not in ("bfloat16", "float32"):
             raise ValueError("dtype must be 'bfloat16' or 'float32'")
         if not torch.cuda.is_available():
@@ -161,7 +161,8 @@ class CausalLM:
         # portions run on the tensor cores with bfloat16 operands and fp32 accumulation.  Norms, scores, the router, the
         # pages and the residual stream are float32 in both.
         self.engine = LMEngine(self.layers, weights["embed"], weights["head"], final_norm, width=cfg.width, vocab=cfg.vocab,
-                               taps=cfg.canon.taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype)
+                               taps=cfg.canon.taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype,
+                               step_graphs=step_graphs)
         self._draws = 0
 
     @classmethod

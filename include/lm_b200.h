@@ -71,6 +71,8 @@ typedef struct lm_b200_model {
     const void *embed, *head;      /* [vocab][width] */
     lm_b200_norm final_norm;
     const int32_t *page_table;     /* device, [n_slots][max_pages] */
+    int32_t step_graphs;           /* != 0: steps of a few rows (decoding) replay a CUDA graph captured at their first use */
+    int32_t reserved;
 } lm_b200_model;
 
 typedef struct lm_b200_engine lm_b200_engine;
