@@ -85,6 +85,7 @@ struct lm_b200_engine {
     // bf16 operands of the tensor-core products (bfloat16 precision only)
     void *hb, *attb, *packb, *midb, *smidb, *hwb;
     float* split_ws;                             // partial results of the key splits of a few rows' attention
+    unsigned* split_arrived;                     // ... and their arrival counters (zero between launches)
     // steps of a few rows are captured once per (rows, sequences, wanted) into a CUDA graph over these fixed buffers
     int32_t* step_static = nullptr;
     float* logits_static = nullptr;
@@ -175,7 +176,7 @@ int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void*
                                  v.rm, M, st));
     const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
     const bool tc_o = tensor_path(e, M, D, nq);
-    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, tc_o ? e->attb : nullptr, e->split_ws, M, st));
+    LCK(lm::launch_sink_attention(e->qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, e->att, tc_o ? e->attb : nullptr, e->split_ws, e->split_arrived, M, st));
     if (tc_o) {
         if (fuse_x) {
             const dia::GemmEpilogue ep{fuse_x, l.norm_mix_out.w, l.norm_mix_out.b, l.norm_mix_out.alpha};
@@ -303,6 +304,9 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     for (const lm_b200_layer& l : e->layers)
         split = std::max(split, (size_t)lm::kAttnRowsKernelMax * l.heads * lm::kAttnSplitsMax * (l.dim + 2) * 4);
     const size_t o_split = take(split);
+    size_t max_heads = 1;
+    for (const lm_b200_layer& l : e->layers) max_heads = std::max(max_heads, (size_t)l.heads);
+    const size_t arrived_bytes = (size_t)lm::kAttnRowsKernelMax * max_heads * 4, o_arrived = take(arrived_bytes);
     const size_t o_step = take((size_t)(8 * lm::kRowsKernelMax) * 4), o_logits = take((size_t)lm::kRowsKernelMax * m.vocab * 4);
     const bool tcb = m.precision == LM_B200_PRECISION_BF16;
     const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
@@ -323,6 +327,13 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->hb = b + o_hb; e->attb = b + o_attb; e->packb = b + o_packb; e->midb = b + o_midb; e->smidb = b + o_smidb;
     e->hwb = b + o_hwb;
     e->split_ws = (float*)(b + o_split);
+    e->split_arrived = (unsigned*)(b + o_arrived);
+    if (cudaMemset(e->split_arrived, 0, arrived_bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaFree(e->arena);
+        delete e;
+        return LM_B200_ECUDA;
+    }
     e->step_static = (int32_t*)(b + o_step);
     e->logits_static = (float*)(b + o_logits);
     *out = e;
@@ -467,7 +478,7 @@ int lm_b200_op_attention(lm_b200_engine* e, int layer, float* qk, const int32_t*
     LCK(lm::launch_qk_norm_cache(qk, nq, nk, l.q_norm, l.k_norm, e->m.eps, l.k_pages, l.v_pages, pm, l.kv_heads, l.dim, v.rm, M,
                                  S(stream)));
     const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
-    LCK(lm::launch_sink_attention(qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, out, nullptr, e->split_ws, M, S(stream)));
+    LCK(lm::launch_sink_attention(qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, out, nullptr, e->split_ws, e->split_arrived, M, S(stream)));
     return LM_B200_OK;
 }
 

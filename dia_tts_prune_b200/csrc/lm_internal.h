@@ -46,8 +46,8 @@ cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, con
                                  float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
                                  cudaStream_t st);
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
-                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws, int M,
-                                  cudaStream_t st);
+                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws,
+                                  unsigned* arrived, int M, cudaStream_t st);
 cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st);
 cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign, int top, int E, int pad, const GroupMap& gm,
                              int* slot_of, int max_slots, cudaStream_t st);

@@ -23,7 +23,7 @@
 //   down_combine_rows_kernel   down products of a row's experts and the shared expert, their sum, norm, residual add
 //   router_rows_kernel         router logits, top experts, scores and the assignment maps of a handful of rows
 //   qk_norm_cache_kernel       whole-projection RMS norm of q and k, raw k and normed k scattered into the paged cache
-//   sink_attention_split_kernel / _combine_kernel   softmax attention over the pages for a handful of rows, split over
+//   sink_attention_split_kernel   softmax attention over the pages for a handful of rows, split over
 //                              the keys: per-head temperature, tanh cap, linear distance bias, a window that keeps the
 //                              first tokens, and a value-less sink term in the denominator
 //   sink_attention_tile_kernel the same for prompt portions: 64 queries share the key / value tiles (flash-style)
@@ -290,16 +290,16 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const 
     const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(arow) & 15) == 0);
     if (vec) {
-        // four 16-byte weight loads per lane in flight before their products (the sum keeps its order: k ascending)
-        for (int k0 = lane * 8; k0 < K; k0 += 1024) {
-            uint4 wv[4];
+        // eight 16-byte weight loads per lane in flight before their products (the sum keeps its order: k ascending)
+        for (int k0 = lane * 8; k0 < K; k0 += 2048) {
+            uint4 wv[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int k = k0 + 256 * u;
                 wv[u] = k < K ? *reinterpret_cast<const uint4*>(wrow + k) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int k = k0 + 256 * u;
                 if (k >= K) break;
                 const float4 x0 = *reinterpret_cast<const float4*>(arow + k);
@@ -403,7 +403,7 @@ down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat
 
 // One CTA per row: router logits z = h . Wr^T (fp32), the `top` largest in descending order (ties: the lower index),
 // scores sigmoid(z), and the assignment maps of the row kernels: slot r * top + t holds (row r, expert, score).
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __restrict__ Wr, int E, int top,
                    float* __restrict__ z_out, int* __restrict__ a_row, float* __restrict__ a_scale, int* __restrict__ a_expert,
                    int* __restrict__ slot_of, int* __restrict__ n_slots) {
@@ -476,21 +476,60 @@ __global__ void qk_norm_cache_kernel(float* __restrict__ qk, int nq, int nk, con
 // Attention of a few rows (decoding), split over the keys.  Query position i sees key j <= i when i - j < window or
 // j < keep_first (window <= 0: every j <= i).  score = cap * tanh(q.k * scale * temp_h / cap) - slope_h * (i - j)
 // (cap <= 0: no cap).  One CTA per (row, up to HG query heads of one key/value head, split of the visible keys): a warp
-// takes every fourth key of the split, reads its key and value rows once for all HG heads (lanes over the head size,
+// takes every eighth key of the split, reads its key and value rows once for all HG heads (lanes over the head size,
 // coalesced), and keeps a running (maximum, denominator, weighted value sum) per head; the CTA's warps are merged and
-// written as one partial per (row, head, split).  sink_attention_combine_kernel merges the splits in their fixed order
-// and adds the sink: exp(sink_h) joins the denominator only (no key, no value).
-constexpr int kSplitThreads = 128, kSplitWarps = kSplitThreads / 32;
+// written as one partial per (row, head, split).  The CTA that arrives last at its (row, head chunk) merges the splits in
+// their fixed order and adds the sink: exp(sink_h) joins the denominator only (no key, no value).
+constexpr int kSplitThreads = 256, kSplitWarps = kSplitThreads / 32;
 constexpr int kAttnMaxDimPerLane = 8;                         // head dim <= 256
+
+// merges the S partial results of each of the nh <= 4 heads h0 .. of row r in their fixed order and adds the sink; one
+// CTA of at least 4 warps: warp w weighs the splits of head h0 + w, then all threads sum.  scratch: >= 4 * 33 floats
+__device__ __forceinline__ void combine_splits(const float* __restrict__ part, int S, int heads, int dim,
+                                               const float* __restrict__ sink, float* __restrict__ out,
+                                               __nv_bfloat16* __restrict__ out_b, int r, int h0, int nh, float* scratch) {
+    static_assert(kAttnSplitsMax <= 32, "one lane per split");
+    const size_t stride = (size_t)(dim + 2);
+    const float* src0 = part + (size_t)(r * heads + h0) * S * stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();                                          // the scratch's previous use is over
+    if (warp < nh) {
+        const float* src = src0 + (size_t)warp * S * stride;
+        float* wgt = scratch + warp * 33;                     // exp(m_s - m) per split, 0 for an empty one; [32] = 1 / l
+        const float ms = lane < S ? __ldcg(src + lane * stride) : -CUDART_INF_F;
+        const float ls = lane < S ? __ldcg(src + lane * stride + 1) : 0.f;
+        const float sk = sink ? sink[h0 + warp] : -CUDART_INF_F;
+        const float m = fmaxf(sk, warp_max(ms));
+        const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - m);
+        float l = sink ? expf(sk - m) : 0.f;
+        for (int t = 0; t < S; ++t) l += __shfl_sync(0xffffffffu, ls * w, t);
+        wgt[lane] = lane < S ? w : 0.f;
+        if (lane == 0) wgt[32] = l > 0.f ? 1.0f / l : 0.f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nh * dim; idx += blockDim.x) {
+        const int hh = idx / dim, c = idx - hh * dim;
+        const float* src = src0 + (size_t)hh * S * stride + 2 + c;
+        const float* wgt = scratch + hh * 33;
+        float o = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < S; ++s) o = fmaf(__ldcg(src + s * stride), wgt[s], o);
+        o *= wgt[32];
+        out[((size_t)r * heads + h0 + hh) * dim + c] = o;
+        if (out_b) out_b[((size_t)r * heads + h0 + hh) * dim + c] = __float2bfloat16_rn(o);
+    }
+}
 
 template <int HG>
 __global__ void __launch_bounds__(kSplitThreads)
 sink_attention_split_kernel(const float* __restrict__ qk, int q_stride, const float* __restrict__ kcache,
                             const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size,
                             int heads, int kv_heads, int dim, float scale, float cap, const float* __restrict__ temp,
-                            const float* __restrict__ slopes, int window, int keep_first, const int* __restrict__ row_slot,
-                            const int* __restrict__ row_pos, float* __restrict__ part) {
+                            const float* __restrict__ slopes, const float* __restrict__ sink, int window, int keep_first,
+                            const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ part,
+                            unsigned* __restrict__ arrived, float* __restrict__ out, __nv_bfloat16* __restrict__ out_b) {
     __shared__ float sm_m[kSplitWarps][HG], sm_l[kSplitWarps][HG];
+    __shared__ bool is_last;
     __shared__ float sm_acc[kSplitWarps][HG][32 * kAttnMaxDimPerLane];
     const int r = blockIdx.x, S = gridDim.z, sp = blockIdx.z;
     const int group = heads / kv_heads, chunks = (group + HG - 1) / HG;
@@ -582,37 +621,21 @@ sink_attention_split_kernel(const float* __restrict__ qk, int q_stride, const fl
             dst[2 + c] = o;
         }
     }
-}
-
-__global__ void __launch_bounds__(128)
-sink_attention_combine_kernel(const float* __restrict__ part, int S, int heads, int dim, const float* __restrict__ sink,
-                              float* __restrict__ out, __nv_bfloat16* __restrict__ out_b) {
-    const int r = blockIdx.x, h = blockIdx.y;
-    const float* src = part + (size_t)(r * heads + h) * S * (dim + 2);
-    static_assert(kAttnSplitsMax <= 32, "one lane per split");
-    __shared__ float wgt[kAttnSplitsMax];                    // exp(m_s - m) per split, 0 for an empty one
-    __shared__ float inv_s;
-    if (threadIdx.x < 32) {                                   // one warp: S <= kAttnSplitsMax = 32 splits, one per lane
-        const int s = threadIdx.x;
-        const float ms = s < S ? src[(size_t)s * (dim + 2)] : -CUDART_INF_F;
-        const float ls = s < S ? src[(size_t)s * (dim + 2) + 1] : 0.f;
-        const float m = fmaxf(sink ? sink[h] : -CUDART_INF_F, warp_max(ms));
-        const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - m);
-        // the denominator in the fixed order of the splits
-        float l = sink ? expf(sink[h] - m) : 0.f;
-        for (int t = 0; t < S; ++t) l += __shfl_sync(0xffffffffu, ls * w, t);
-        if (s < S) wgt[s] = w;
-        if (s == 0) inv_s = l > 0.f ? 1.0f / l : 0.f;
+    // the split that arrives last at its (row, head chunk) merges all of them: no second launch.  The counter goes back
+    // to zero for the next step.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* cnt = arrived + (size_t)r * gridDim.y + blockIdx.y;
+        const unsigned seen = atomicAdd(cnt, 1u);
+        is_last = seen == (unsigned)S - 1u;
+        if (is_last) *cnt = 0u;
     }
     __syncthreads();
-    const float inv = inv_s;
-    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-        float o = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < S; ++s) o = fmaf(src[(size_t)s * (dim + 2) + 2 + c], wgt[s], o);
-        out[((size_t)r * heads + h) * dim + c] = o * inv;
-        if (out_b) out_b[((size_t)r * heads + h) * dim + c] = __float2bfloat16_rn(o * inv);
-    }
+    if (!is_last) return;
+    __threadfence();
+    static_assert(HG <= kSplitWarps, "one warp per head in the merge");
+    combine_splits(part, S, heads, dim, sink, out, out_b, r, h0, nh, sm_acc[0][0]);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -1045,7 +1068,7 @@ cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, co
 
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
                                int* slot_of, cudaStream_t st) {
-    router_rows_kernel<<<M, 128, E * sizeof(float), st>>>(h, D, reinterpret_cast<const __nv_bfloat16*>(Wr), E, top, z, gm.a_row,
+    router_rows_kernel<<<M, 256, E * sizeof(float), st>>>(h, D, reinterpret_cast<const __nv_bfloat16*>(Wr), E, top, z, gm.a_row,
                                                           gm.a_scale, gm.a_expert, slot_of, gm.n_slots);
     return cudaGetLastError();
 }
@@ -1082,7 +1105,7 @@ static cudaError_t launch_attention_tiles(const float* qk, int q_stride, const f
 template <int HG>
 static cudaError_t launch_attention_splits(const float* qk, int q_stride, const float* kcache, const float* vcache,
                                            const PageMap& pm, const AttnShape& a, const RowMeta& rm, float* out,
-                                           __nv_bfloat16* out_b, int M, float* split_ws, cudaStream_t st) {
+                                           __nv_bfloat16* out_b, int M, float* split_ws, unsigned* arrived, cudaStream_t st) {
     const int group = a.heads / a.kv_heads, chunks = (group + HG - 1) / HG;
     // enough CTAs for two per SM, at least 16 keys per split where the window bounds the keys
     const long long max_keys = a.window > 0 ? (long long)a.window + a.keep_first : (long long)pm.max_pages * pm.page_size;
@@ -1091,18 +1114,15 @@ static cudaError_t launch_attention_splits(const float* qk, int q_stride, const 
     S = (int)std::max<long long>(1, std::min<long long>(std::min(S, kAttnSplitsMax), (max_keys + 15) / 16));
     sink_attention_split_kernel<HG><<<dim3(M, a.kv_heads * chunks, S), kSplitThreads, 0, st>>>(
         qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
-        a.temp, a.slopes, a.window, a.keep_first, rm.slot, rm.pos, split_ws);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    sink_attention_combine_kernel<<<dim3(M, a.heads), 128, 0, st>>>(split_ws, S, a.heads, a.dim, a.sink, out, out_b);
+        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, split_ws, arrived, out, out_b);
     return cudaGetLastError();
 }
 
 // a step of a few rows (decoding) splits every row's keys over CTAs; longer steps run the tiled kernel.
-// split_ws: kRowsKernelMax * heads * kAttnSplitsMax * (dim + 2) floats
+// split_ws: kRowsKernelMax * heads * kAttnSplitsMax * (dim + 2) floats; arrived: kRowsKernelMax * heads zeroed counters
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
-                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws, int M,
-                                  cudaStream_t st) {
+                                  const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws,
+                                  unsigned* arrived, int M, cudaStream_t st) {
     if (a.dim > 32 * kAttnMaxDimPerLane || a.heads % a.kv_heads) return cudaErrorNotSupported;
     __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out_bf16);
     if (M > kAttnRowsKernelMax) {
@@ -1114,9 +1134,9 @@ cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kc
         }
     }
     const int group = a.heads / a.kv_heads;
-    if (group >= 4) return launch_attention_splits<4>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, st);
-    if (group >= 2) return launch_attention_splits<2>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, st);
-    return launch_attention_splits<1>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, st);
+    if (group >= 4) return launch_attention_splits<4>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, arrived, st);
+    if (group >= 2) return launch_attention_splits<2>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, arrived, st);
+    return launch_attention_splits<1>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, arrived, st);
 }
 
 cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st) {
