@@ -542,7 +542,7 @@ def run_lm(args) -> None:
         weights = SY.pubopel_weights(cfg, WEIGHT_SEED, dev)
         T, ctx = args.lm_prompt, args.lm_context
         model = CausalLM(PubopelConfig.model_validate(cfg), weights, dtype="bfloat16", device=dev,
-                         max_tokens=max(T, 8 * (ctx + 32 * (K + 2))) + 64, max_sequences=8, page_size=64, max_rows=1024)
+                         max_tokens=max(T, 8 * (ctx + 32 * (K + 2))) + 64, max_sequences=8, page_size=64, max_rows=args.lm_rows)
         del weights
         D, H, G, d = sz["width"], sz["heads"], sz["kv_heads"], sz["dim"]
         nq, nk, F, Sf, E, top, V, L = H * d, G * d, sz["expert_ff"], sz["shared_ff"], sz["experts"], sz["top"], sz["vocab"], sz["layers"]
@@ -551,14 +551,14 @@ def run_lm(args) -> None:
         toks = torch.randint(0, V, (T,), generator=g).tolist()
         res = {"config": sz}
 
-        # -- prefill: one prompt of T tokens through the step function (portions of 1024 rows), logits of the last token
+        # -- prefill: one prompt of T tokens through the step function (portions of --lm-rows rows), logits of the last token
         def prefill():
             model.run_step([{"id": "p", "tokens": toks, "want": [T - 1]}], ["p"])
         ms = _event_ms(prefill, W, K, flush)
         seen = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(T))
         flops = L * (2.0 * T * D * (nq + nk) + 2.0 * T * nq * D + 2.0 * T * D * E + top * 6.0 * T * D * F + 6.0 * T * D * Sf
                      + 4.0 * d * H * seen) + 2.0 * D * V
-        res["prefill"] = {"tokens": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "model_tflops": flops / ms / 1e9,
+        res["prefill"] = {"tokens": T, "rows_per_step": args.lm_rows, "ms": ms, "tokens_per_s": T / ms * 1e3, "model_tflops": flops / ms / 1e9,
                           "frac_of_bf16_peak": flops / ms / 1e9 / tf}
 
         # -- decode: B sequences of `ctx` tokens each, one token per sequence per step, teacher-forced, device-timed
@@ -590,7 +590,7 @@ def run_lm(args) -> None:
                                "new_tokens_per_s": sum(len(o) for o in outs) / wall}
 
         # -- kernels alone, beside Dia's at equal size
-        M = 1024
+        M = min(args.lm_rows, T)
         kern = {}
         for label, (N_, K_) in {"qk_proj": (nq + nk, D), "o_proj": (D, nq), "shared_gate_up": (2 * Sf, D)}.items():
             a = torch.randn(M, K_, device=dev)
@@ -606,12 +606,12 @@ def run_lm(args) -> None:
                                                                            "experts": 1, "top": 1, "expert_ff": 8, "shared_ff": None})),
                         SY.pubopel_weights(SY.pubopel_config(**{**sz, "layers": 1, "window": None, "vocab": 256, "experts": 1,
                                                                 "top": 1, "expert_ff": 8, "shared_ff": None}), 3, dev),
-                        dtype="float32", device=dev, max_tokens=T + 64, max_sequences=2, page_size=64, max_rows=1024)
+                        dtype="float32", device=dev, max_tokens=T + 64, max_sequences=2, page_size=64, max_rows=args.lm_rows)
         qk = torch.randn(T, nq + nk, device=dev)
         def lm_attn():
             seq = full.state.open("a")
-            for r0 in range(0, T, 1024):
-                n = min(1024, T - r0)
+            for r0 in range(0, T, args.lm_rows):
+                n = min(args.lm_rows, T - r0)
                 full.state.reserve(seq, n)
                 full.engine.op_attention(0, qk[r0:r0 + n], [(seq, n, r0)])
                 full.state.advance(seq, n)
@@ -661,6 +661,7 @@ def main():
                          "(Pubopel, random weights) at layer sizes of a real model, beside Dia's kernels at equal size")
     ap.add_argument("--lm-sizes", default="", help="--lm: comma-separated subset of " + ",".join(LM_SIZES))
     ap.add_argument("--lm-prompt", type=int, default=4096, help="--lm: prompt tokens of the prefill measurement")
+    ap.add_argument("--lm-rows", type=int, default=4096, help="--lm: most rows of one engine step (longer prompts run in portions)")
     ap.add_argument("--lm-context", type=int, default=1024, help="--lm: tokens each sequence holds before the decode measurement")
     args = ap.parse_args()
     if args.lm:

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 
+import numpy as np
 import torch
 
 from . import _lm_lib
@@ -74,22 +75,27 @@ class LMEngine:
     # ---- one launch sequence over <= max_rows rows -----------------------------------------------------------
     def _pack(self, parts: list[tuple[Sequence, list[int], int, list[int]]]) -> tuple[torch.Tensor, int, int, int]:
         """parts: (sequence, tokens, position of the first token, wanted indexes into tokens) -> the step buffer."""
-        tok, slot, pos, start, s_slot, s_row0, s_count, want = [], [], [], [], [], [], [], []
-        for seq, tokens, p0, w in parts:
-            r0 = len(tok)
+        n_rows = sum(len(t) for _, t, _, _ in parts)
+        S = len(parts)
+        want = [k for _, _, _, w in parts for k in w]
+        buf = np.empty(4 * n_rows + 3 * S + len(want), dtype=np.int32)
+        tok, slot, pos, start = (buf[i * n_rows:(i + 1) * n_rows] for i in range(4))
+        meta, r0, at = buf[4 * n_rows:], 0, 0
+        for s, (seq, tokens, p0, w) in enumerate(parts):
             n = len(tokens)
-            tok += tokens
-            slot += [seq.slot] * n
-            pos += range(p0, p0 + n)
-            start += [p0] * n
-            s_slot.append(seq.slot)
-            s_row0.append(r0)
-            s_count.append(n)
-            want += [r0 + k for k in w]
-        buf = torch.tensor(tok + slot + pos + start + s_slot + s_row0 + s_count + want, dtype=torch.int32)
-        if buf.numel() > 4096:                                  # a long step: asynchronous copy from pinned memory
-            buf = buf.pin_memory()
-        return buf.to(self.device, non_blocking=True), len(tok), len(parts), len(want)
+            tok[r0:r0 + n] = tokens
+            slot[r0:r0 + n] = seq.slot
+            pos[r0:r0 + n] = np.arange(p0, p0 + n, dtype=np.int32)
+            start[r0:r0 + n] = p0
+            meta[s], meta[S + s], meta[2 * S + s] = seq.slot, r0, n
+            for k in w:
+                meta[3 * S + at] = r0 + k
+                at += 1
+            r0 += n
+        t = torch.from_numpy(buf)
+        if buf.size > 4096:                                     # a long step: asynchronous copy from pinned memory
+            t = t.pin_memory()
+        return t.to(self.device, non_blocking=True), n_rows, S, len(want)
 
     def _forward(self, parts, logits_out: torch.Tensor | None, layers_out: torch.Tensor | None = None) -> None:
         buf, M, S, W = self._pack(parts)
