@@ -460,6 +460,52 @@ def test_replayed_step_graphs_give_the_same_bits_as_plain_launches():
     assert torch.equal(ga, gb)
 
 
+# ---- made-up configurations of many shapes ---------------------------------------------------------------------------------
+def drawn_config(seed):
+    """Sizes drawn per layer: group sizes 1 / 2 / 3 / 5 / 6, head sizes on and off the vector and tile widths, windows of
+    one token up to longer than the prompt, a kept prefix longer than the window, one expert, as many chosen experts as
+    there are, more experts than lanes, many taps, widths the tensor-core kernel takes and widths it does not."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([40, 64, 100, 136])
+    layers = []
+    for _ in range(r.choice([2, 3, 4])):
+        kv, group, dim = r.choice([1, 2, 3]), r.choice([1, 2, 3, 5, 6]), r.choice([8, 16, 20, 48, 72, 128])
+        window = r.choice([None, 1, 5, 17, 64, 200])
+        mixer = {"heads": kv * group, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": r.choice([0.05, 0.3, 1.0]),
+                 "softcap": r.choice([None, 5.0, 50.0]),
+                 "mask": None if window is None else {"size": window, "keep_first": r.choice([0, 1, 3, 30])}}
+        mlp = None
+        if r.random() < 0.8:
+            experts = r.choice([1, 2, 6, 40])
+            mlp = {"kind": "moe", "expert": {"ff": r.choice([8, 12, 40])},
+                   "router": {"experts": experts, "top": r.choice([1, min(2, experts), min(3, experts), experts if experts <= 6 else 4])},
+                   "shared": r.choice([None, {"ff": 16}, {"ff": 33}])}
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Pubopel", "vocab": r.choice([50, 97, 128, 260]), "width": width,
+            "canon": {"taps": r.choice([1, 2, 3, 5, 16])}, "norm": {"eps": r.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_drawn_configurations_whole_portioned_and_decoded(seed):
+    cfg = drawn_config(seed)
+    lo, hi, w = build_pair(cfg, 100 + seed, max_tokens=256)
+    toks = tokens(cfg, 75, seed)
+    ref, streams = O.forward(cfg, w, toks, dtype=torch.float64, keep_layers=True)
+    close(whole(hi, "a", toks), ref)
+    got, at = [], 0
+    for n in (37, 2, 20, 3):                                    # portions, then single tokens
+        got.append(hi.run_step([{"id": "p", "tokens": toks[at:at + n], "want": list(range(n))}]))
+        at += n
+    for t in range(at, 75):
+        got.append(hi.run_step([{"id": "p", "tokens": [toks[t]], "want": [0]}], ["p"] if t == 74 else []))
+    close(torch.cat(got), ref)
+    # bfloat16 products: the residual stream after the first layer, where a router near-tie that went the other way
+    # moves its own row only (further on, long taps carry such a row into its neighbours)
+    _, got_streams = whole(lo, "b", toks, keep_layers=True)
+    mostly_close(got_streams[0], streams[0], 4e-2, share=0.8)
+
+
 # ---- generation through the scheduler -------------------------------------------------------------------------------------
 def test_greedy_generation_through_the_scheduler():
     cfg = small_config()
