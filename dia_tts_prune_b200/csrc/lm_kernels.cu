@@ -72,17 +72,6 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     for (int i = 0; i < nw; ++i) t += red[i];
     return t;
 }
-__device__ __forceinline__ float block_max(float v, float* red) {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    v = warp_max(v);
-    __syncthreads();
-    if (lane == 0) red[w] = v;
-    __syncthreads();
-    float t = -CUDART_INF_F;
-    for (int i = 0; i < nw; ++i) t = fmaxf(t, red[i]);
-    return t;
-}
-
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------------
