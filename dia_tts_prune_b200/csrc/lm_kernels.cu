@@ -703,27 +703,56 @@ sink_attention_tile_kernel(const float* __restrict__ qk, int q_stride, const flo
         const int n_keep = window > 0 ? min(keep_first, lo) : 0;
         for (int phase = 0; phase < 2; ++phase) {
             const int k_begin = phase == 0 ? 0 : lo, k_end = phase == 0 ? n_keep : p_last + 1;
+            // Head sizes up to 128 keep the next key / value tile in registers while the current one is multiplied (the
+            // gather's latency hides behind the arithmetic); larger heads have no registers to spare and load in place.
+            constexpr bool kAhead = NC <= 2;
+            constexpr int PF = kAhead ? kTK * C4 / kTileThreads : 1;
+            float4 kreg[PF], vreg[PF];
+            auto gather = [&](int j0, int it, float4& kk, float4& vv) {
+                const int i = tid + it * kTileThreads;
+                const int r = i / C4, c = (i - r * C4) * 4, j = j0 + r;
+                kk = make_float4(0.f, 0.f, 0.f, 0.f);
+                vv = kk;
+                if (j < k_end && c < dim) {
+                    const size_t at = (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim + c;
+                    if (vec) {
+                        kk = *reinterpret_cast<const float4*>(kcache + at);
+                        vv = *reinterpret_cast<const float4*>(vcache + at);
+                    } else {
+                        kk.x = kcache[at]; vv.x = vcache[at];
+                        if (c + 1 < dim) { kk.y = kcache[at + 1]; vv.y = vcache[at + 1]; }
+                        if (c + 2 < dim) { kk.z = kcache[at + 2]; vv.z = vcache[at + 2]; }
+                        if (c + 3 < dim) { kk.w = kcache[at + 3]; vv.w = vcache[at + 3]; }
+                    }
+                }
+            };
+            auto put = [&](int it, const float4& kk, const float4& vv) {
+                const int i = tid + it * kTileThreads;
+                const int r = i / C4, c = (i - r * C4) * 4;
+                *reinterpret_cast<float4*>(Ks + r * QS + c) = kk;
+                *reinterpret_cast<float4*>(Vs + r * DP + c) = vv;
+            };
+            if (kAhead && k_begin < k_end) {
+#pragma unroll
+                for (int it = 0; it < PF; ++it) gather(k_begin, it, kreg[it], vreg[it]);
+            }
             for (int j0 = k_begin; j0 < k_end; j0 += kTK) {
                 __syncthreads();                              // the previous tile is consumed
-                for (int i = tid; i < kTK * C4; i += kTileThreads) {
-                    const int r = i / C4, c = (i - r * C4) * 4, j = j0 + r;
-                    float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
-                    if (j < k_end && c < dim) {
-                        const size_t at = (((size_t)pages[j / page_size] * kv_heads + g) * page_size + (j % page_size)) * dim + c;
-                        if (vec) {
-                            kk = *reinterpret_cast<const float4*>(kcache + at);
-                            vv = *reinterpret_cast<const float4*>(vcache + at);
-                        } else {
-                            kk.x = kcache[at]; vv.x = vcache[at];
-                            if (c + 1 < dim) { kk.y = kcache[at + 1]; vv.y = vcache[at + 1]; }
-                            if (c + 2 < dim) { kk.z = kcache[at + 2]; vv.z = vcache[at + 2]; }
-                            if (c + 3 < dim) { kk.w = kcache[at + 3]; vv.w = vcache[at + 3]; }
-                        }
+                if (kAhead) {
+#pragma unroll
+                    for (int it = 0; it < PF; ++it) put(it, kreg[it], vreg[it]);
+                } else {
+                    for (int it = 0; it < kTK * C4 / kTileThreads; ++it) {
+                        float4 kk, vv;
+                        gather(j0, it, kk, vv);
+                        put(it, kk, vv);
                     }
-                    *reinterpret_cast<float4*>(Ks + r * QS + c) = kk;
-                    *reinterpret_cast<float4*>(Vs + r * DP + c) = vv;
                 }
                 __syncthreads();
+                if (kAhead && j0 + kTK < k_end) {
+#pragma unroll
+                    for (int it = 0; it < PF; ++it) gather(j0 + kTK, it, kreg[it], vreg[it]);
+                }
                 // ---- S = Q K^T: rows ty*4 + i, keys tx + 16 j ----
                 float sc[4][4];
 #pragma unroll
