@@ -97,6 +97,7 @@ struct lm_b200_engine {
 namespace {
 
 constexpr int kTensorRowsMin = 32;               // rows of a step from which its products run on the tensor cores
+constexpr int kHeadTensorRowsMin = 4;            // wanted rows from which the head does
 
 // assignment slots of `rows` rows when every expert group is padded to `pad` slots
 int slots_bound(int rows, int top, int experts, int pad) {
@@ -382,7 +383,10 @@ int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_wan
         }
     }
     if (n_want > 0) {
-        const bool tc = tensor_path(e, n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
+        // the head is the largest single weight stream: from kHeadTensorRowsMin wanted rows on (a batch of decoding
+        // sequences) the tensor-core kernel reads it once for all rows, where the row kernel reads it once per row
+        const bool tc = e->m.precision == LM_B200_PRECISION_BF16 && n_want >= kHeadTensorRowsMin &&
+                        dia::gemm_tcgen05_shape_ok(n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
         LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
         if (tc)
             LCK(dia::launch_gemm_tcgen05_bf16(e->hwb, 1, e->m.head, e->m.vocab, logits_out, n_want, e->m.vocab, D, kPlain, nullptr, st));

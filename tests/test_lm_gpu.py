@@ -435,6 +435,21 @@ def test_expert_groups_on_the_tensor_cores(rows):
         close(lo.engine.op_ff(layer, h.cuda()), O.routed_experts(h.double(), p, lc["mlp"]), 2e-2)
 
 
+def test_batched_decoding_with_bfloat16_products():
+    """Five sequences decode side by side: from four wanted rows on the head runs on the tensor cores (inside the replayed
+    graph); every sequence stays within bfloat16 rounding of the float32 engine fed the same tokens."""
+    cfg = wide_config()
+    lo, hi, w = build_pair(cfg, 45)
+    prompts = [tokens(cfg, n, 50 + n) for n in (9, 20, 33, 5, 14)]
+    tail = tokens(cfg, 6, 60)
+    for m in (lo, hi):
+        for i, p in enumerate(prompts):
+            m.run_step([{"id": f"s{i}", "tokens": p, "want": []}])
+    for t in tail:
+        step = [{"id": f"s{i}", "tokens": [t], "want": [0]} for i in range(5)]
+        mostly_close(lo.run_step(step), hi.run_step(step).cpu(), 4e-2, share=0.8)
+
+
 def test_replayed_step_graphs_give_the_same_bits_as_plain_launches():
     from dia_tts_prune_b200.lm_config import PubopelConfig
     from dia_tts_prune_b200.lm_engine import launch_count
