@@ -50,6 +50,12 @@ __device__ __forceinline__ float bf(const __nv_bfloat16 v) { return __bfloat162f
 
 __device__ __forceinline__ float dyt(float x, float alpha, float w, float b) { return fmaf(tanhf(alpha * x), w, b); }
 
+// Programmatic dependent launch: a kernel of a short step lets the next one start as soon as it runs itself
+// (pdl_release) and reads what earlier kernels wrote - or writes anything - only after pdl_wait.  Before the wait a
+// kernel may fetch weights, which no kernel writes.  Launched without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -77,6 +83,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void embed_rows_bf16_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
                                        float* __restrict__ out, int V, int D) {
+    pdl_release();
+    pdl_wait();
     const int r = blockIdx.x;
     const int id = ids[r];
     const bool ok = id >= 0 && id < V;
@@ -144,6 +152,8 @@ __global__ void dyt_tapmix_seq_kernel(const float* __restrict__ x, const float* 
                                       const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
                                       const int* __restrict__ seq_count, const int* __restrict__ row_pos,
                                       float* __restrict__ out, int D) {
+    pdl_release();
+    pdl_wait();
     const int s = blockIdx.x, T1 = taps > 0 ? taps - 1 : 0;
     const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s];
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
@@ -273,8 +283,9 @@ linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
 // ---- the row kernels: a step of a few rows (decoding).  One warp per output element; the weights stream once per row,
 // 16 bytes per lane.  Their epilogues do what the next kernel of a long step would: the DynamicTanh + residual add, the
 // gate, the sum over a row's experts.
+// wait_first: the first weight loads go out before pdl_wait, the activations are read after it
 __device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const __nv_bfloat16* __restrict__ wrow, int K, int lda,
-                                          float sc, int lane) {
+                                          float sc, int lane, bool wait_first = false) {
     float acc = 0.f;
     const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(arow) & 15) == 0);
@@ -287,6 +298,7 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const 
                 const int k = k0 + 256 * u;
                 wv[u] = k < K ? *reinterpret_cast<const uint4*>(wrow + k) : make_uint4(0u, 0u, 0u, 0u);
             }
+            if (wait_first) { pdl_wait(); wait_first = false; }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int k = k0 + 256 * u;
@@ -305,8 +317,10 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const 
             }
         }
     } else {
+        if (wait_first) pdl_wait();
         for (int k = lane; k < K; k += 32) acc = fmaf(arow[k] * sc, bf(wrow[k]), acc);
     }
+    if (wait_first) pdl_wait();                               // (K == 0: nothing was loaded)
     return warp_sum(acc);
 }
 
@@ -316,6 +330,9 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
                    float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
                    const float* __restrict__ a_scale, const int* __restrict__ a_expert, const int* __restrict__ n_slots,
                    float* __restrict__ res_x, const float* __restrict__ nw, const float* __restrict__ nb, float alpha) {
+    pdl_release();
+    const bool mapped = a_row || a_scale || a_expert || n_slots;      // the maps are an earlier kernel's output
+    if (mapped) pdl_wait();
     const int a = blockIdx.y;
     const int m_end = n_slots ? min(M, *n_slots) : M;
     if (a >= m_end) return;
@@ -326,7 +343,7 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     if (n >= N) return;
     const float sc = a_scale ? a_scale[a] : 1.f;
     const __nv_bfloat16* wrow = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
-    const float acc = warp_dot(A + (size_t)src * lda, wrow, K, lda, sc, lane);
+    const float acc = warp_dot(A + (size_t)src * lda, wrow, K, lda, sc, lane, !mapped);
     if (lane == 0) {
         if (res_x) res_x[(size_t)a * ldy + n] += dyt(acc, alpha, nw[n], nb[n]);
         else Y[(size_t)a * ldy + n] = acc;
@@ -341,13 +358,16 @@ gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __r
                   float* __restrict__ mid, int n_assign, int F, int K, const int* __restrict__ a_row,
                   const float* __restrict__ a_scale, const int* __restrict__ a_expert, const __nv_bfloat16* __restrict__ Ws,
                   float* __restrict__ smid, int Sf) {
+    pdl_release();
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int a = blockIdx.y, src, width;
     float sc = 1.f;
     const __nv_bfloat16* wg;
     float* dst;
-    if (a < n_assign) {
+    const bool routed = a < n_assign;                         // the routed slots need the router's maps first
+    if (routed) {
+        pdl_wait();
         src = a_row ? a_row[a] : a;
         if (src < 0 || n >= F) return;
         if (a_scale) sc = a_scale[a];
@@ -363,7 +383,7 @@ gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __r
         dst = smid + (size_t)a * Sf + n;
     }
     const float* arow = A + (size_t)src * lda;
-    const float g = warp_dot(arow, wg, K, lda, sc, lane);
+    const float g = warp_dot(arow, wg, K, lda, sc, lane, !routed);
     const float u = warp_dot(arow, wg + (size_t)width * K, K, lda, sc, lane);
     if (lane == 0) *dst = (g / (1.0f + expf(-g))) * u;
 }
@@ -374,12 +394,14 @@ __global__ void __launch_bounds__(256)
 down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat16* __restrict__ Wd, const int* __restrict__ a_expert,
                          int top, const float* __restrict__ smid, int Sf, const __nv_bfloat16* __restrict__ Wsd,
                          float* __restrict__ x, int D, const float* __restrict__ nw, const float* __restrict__ nb, float alpha) {
+    pdl_release();
     const int r = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (n >= D) return;
     float v = 0.f;
-    if (smid) v = warp_dot(smid + (size_t)r * Sf, Wsd + (size_t)n * Sf, Sf, Sf, 1.f, lane);
+    if (smid) v = warp_dot(smid + (size_t)r * Sf, Wsd + (size_t)n * Sf, Sf, Sf, 1.f, lane, true);
+    else pdl_wait();
     for (int t = 0; t < top; ++t) {
         const int a = r * top + t;
         v += warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
@@ -397,9 +419,11 @@ router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __re
                    float* __restrict__ z_out, int* __restrict__ a_row, float* __restrict__ a_scale, int* __restrict__ a_expert,
                    int* __restrict__ slot_of, int* __restrict__ n_slots) {
     extern __shared__ float zs[];                             // [E]
+    pdl_release();
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (warp >= E) pdl_wait();                                // (a warp without an expert may still write the maps below)
     for (int e = warp; e < E; e += nwarp) {
-        const float z = warp_dot(h + (size_t)r * D, Wr + (size_t)e * D, D, D, 1.f, lane);
+        const float z = warp_dot(h + (size_t)r * D, Wr + (size_t)e * D, D, D, 1.f, lane, e == warp);
         if (lane == 0) { zs[e] = z; z_out[(size_t)r * E + e] = z; }
     }
     __syncthreads();
@@ -440,6 +464,8 @@ __global__ void qk_norm_cache_kernel(float* __restrict__ qk, int nq, int nk, con
                                      int kv_heads, int dim, const int* __restrict__ row_slot,
                                      const int* __restrict__ row_pos) {
     __shared__ float red[32];
+    pdl_release();
+    pdl_wait();
     const int r = blockIdx.x;
     float* q = qk + (size_t)r * (nq + nk);
     float* k = q + nq;
@@ -520,6 +546,8 @@ sink_attention_split_kernel(const float* __restrict__ qk, int q_stride, const fl
     __shared__ float sm_m[kSplitWarps][HG], sm_l[kSplitWarps][HG];
     __shared__ bool is_last;
     __shared__ float sm_acc[kSplitWarps][HG][32 * kAttnMaxDimPerLane];
+    pdl_release();
+    pdl_wait();
     const int r = blockIdx.x, S = gridDim.z, sp = blockIdx.z;
     const int group = heads / kv_heads, chunks = (group + HG - 1) / HG;
     const int g = blockIdx.y / chunks, h0 = g * group + (blockIdx.y % chunks) * HG;
@@ -978,6 +1006,8 @@ __global__ void residual_dyt_kernel(float* __restrict__ x, const float* __restri
 __global__ void dyt_gather_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ nw,
                                   const float* __restrict__ nb, float alpha, float* __restrict__ out,
                                   __nv_bfloat16* __restrict__ out_b, int D) {
+    pdl_release();
+    pdl_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         const float v = dyt(x[(size_t)r * D + c], alpha, nw[c], nb[c]);
@@ -1013,9 +1043,24 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int*
 }
 
 // ---- launchers --------------------------------------------------------------------------------------------------------
+// the kernels of a short step are launched with programmatic stream serialization (see pdl_release / pdl_wait)
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 cudaError_t launch_embed(const void* table, const int* ids, float* out, int M, int V, int D, cudaStream_t st) {
-    embed_rows_bf16_kernel<<<M, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(table), ids, out, V, D);
-    return cudaGetLastError();
+    return launch_pdl(embed_rows_bf16_kernel, dim3(M), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(table), ids, out, V, D);
 }
 
 static inline int col_blocks(int D) { return D > 1024 ? (D + 1023) / 1024 : 1; }
@@ -1044,8 +1089,8 @@ cudaError_t launch_linear(const float* A, int lda, const void* W, long long w_ex
     // a few rows, or a few outputs (router logits: the same kernel for every step length, so that the choice of experts
     // does not depend on how a prompt was cut)
     if (M <= kRowsKernelMax || (N <= kRowsKernelMaxOut && M <= 65535))
-        linear_rows_kernel<<<dim3((N + 7) / 8, M), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N, K, a_row, a_scale,
-                                                                 a_expert, n_slots, nullptr, nullptr, nullptr, 0.f);
+        return launch_pdl(linear_rows_kernel, dim3((N + 7) / 8, M), dim3(256), 0, st, A, lda, w, w_expert_stride, Y, ldy, M, N, K,
+                          a_row, a_scale, a_expert, n_slots, (float*)nullptr, (const float*)nullptr, (const float*)nullptr, 0.f);
     else
         linear_tile_kernel<<<dim3((N + BN - 1) / BN, (M + BM - 1) / BM), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N,
                                                                                       K, a_row, a_scale, a_expert, n_slots);
@@ -1055,48 +1100,44 @@ cudaError_t launch_linear(const float* A, int lda, const void* W, long long w_ex
 // ---- the fused forms for a step of a few rows ----
 cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* cw, int taps, float* tail, const SeqMeta& sm,
                                   const RowMeta& rm, int n_seq, float* out, int D, cudaStream_t st) {
-    dyt_tapmix_seq_kernel<<<dim3(n_seq, (D + 127) / 128), 128, 0, st>>>(x, n.w, n.b, n.alpha, cw, taps, tail, sm.slot, sm.row0,
-                                                                        sm.count, rm.pos, out, D);
-    return cudaGetLastError();
+    return launch_pdl(dyt_tapmix_seq_kernel, dim3(n_seq, (D + 127) / 128), dim3(128), 0, st, x, n.w, n.b, n.alpha, cw, taps, tail,
+                      sm.slot, sm.row0, sm.count, rm.pos, out, D);
 }
 
 cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
                                         cudaStream_t st) {
-    linear_rows_kernel<<<dim3((N + 7) / 8, M), 256, 0, st>>>(A, lda, reinterpret_cast<const __nv_bfloat16*>(W), 0, nullptr, N, M, N,
-                                                             K, nullptr, nullptr, nullptr, nullptr, x, n.w, n.b, n.alpha);
-    return cudaGetLastError();
+    return launch_pdl(linear_rows_kernel, dim3((N + 7) / 8, M), dim3(256), 0, st, A, lda, reinterpret_cast<const __nv_bfloat16*>(W),
+                      0LL, (float*)nullptr, N, M, N, K, (const int*)nullptr, (const float*)nullptr, (const int*)nullptr,
+                      (const int*)nullptr, x, n.w, n.b, n.alpha);
 }
 
 cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
                               int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st) {
     const int widest = std::max(F, n_shared_rows > 0 ? Sf : 0);
-    gated_rows_kernel<<<dim3((widest + 7) / 8, n_assign + n_shared_rows), 256, 0, st>>>(
-        A, lda, reinterpret_cast<const __nv_bfloat16*>(W), w_expert_stride, mid, n_assign, F, K, gm ? gm->a_row : nullptr,
-        gm ? gm->a_scale : nullptr, gm ? gm->a_expert : nullptr, reinterpret_cast<const __nv_bfloat16*>(Ws), smid, Sf);
-    return cudaGetLastError();
+    return launch_pdl(gated_rows_kernel, dim3((widest + 7) / 8, n_assign + n_shared_rows), dim3(256), 0, st, A, lda,
+                      reinterpret_cast<const __nv_bfloat16*>(W), w_expert_stride, mid, n_assign, F, K,
+                      gm ? (const int*)gm->a_row : nullptr, gm ? (const float*)gm->a_scale : nullptr,
+                      gm ? (const int*)gm->a_expert : nullptr, reinterpret_cast<const __nv_bfloat16*>(Ws), smid, Sf);
 }
 
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
                                      int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, cudaStream_t st) {
-    down_combine_rows_kernel<<<dim3((D + 7) / 8, M), 256, 0, st>>>(mid, F, reinterpret_cast<const __nv_bfloat16*>(Wd), a_expert, top,
-                                                                   smid, Sf, reinterpret_cast<const __nv_bfloat16*>(Wsd), x, D, n.w,
-                                                                   n.b, n.alpha);
-    return cudaGetLastError();
+    return launch_pdl(down_combine_rows_kernel, dim3((D + 7) / 8, M), dim3(256), 0, st, mid, F,
+                      reinterpret_cast<const __nv_bfloat16*>(Wd), a_expert, top, smid, Sf, reinterpret_cast<const __nv_bfloat16*>(Wsd), x,
+                      D, n.w, n.b, n.alpha);
 }
 
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
                                int* slot_of, cudaStream_t st) {
-    router_rows_kernel<<<M, 256, E * sizeof(float), st>>>(h, D, reinterpret_cast<const __nv_bfloat16*>(Wr), E, top, z, gm.a_row,
-                                                          gm.a_scale, gm.a_expert, slot_of, gm.n_slots);
-    return cudaGetLastError();
+    return launch_pdl(router_rows_kernel, dim3(M), dim3(256), E * sizeof(float), st, h, D, reinterpret_cast<const __nv_bfloat16*>(Wr),
+                      E, top, z, gm.a_row, gm.a_scale, gm.a_expert, slot_of, gm.n_slots);
 }
 
 cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,
                                  float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
                                  cudaStream_t st) {
-    qk_norm_cache_kernel<<<M, 256, 0, st>>>(qk, nq, nk, qw, kw, eps, kcache, vcache, pm.table, pm.max_pages, pm.page_size,
-                                            kv_heads, dim, rm.slot, rm.pos);
-    return cudaGetLastError();
+    return launch_pdl(qk_norm_cache_kernel, dim3(M), dim3(256), 0, st, qk, nq, nk, qw, kw, eps, kcache, vcache, pm.table,
+                      pm.max_pages, pm.page_size, kv_heads, dim, rm.slot, rm.pos);
 }
 
 template <int NC>
@@ -1130,10 +1171,9 @@ static cudaError_t launch_attention_splits(const float* qk, int q_stride, const 
     const int others = M * a.kv_heads * chunks;
     int S = (2 * 148 + others - 1) / others;
     S = (int)std::max<long long>(1, std::min<long long>(std::min(S, kAttnSplitsMax), (max_keys + 15) / 16));
-    sink_attention_split_kernel<HG><<<dim3(M, a.kv_heads * chunks, S), kSplitThreads, 0, st>>>(
-        qk, q_stride, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap,
-        a.temp, a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, split_ws, arrived, out, out_b);
-    return cudaGetLastError();
+    return launch_pdl(sink_attention_split_kernel<HG>, dim3(M, a.kv_heads * chunks, S), dim3(kSplitThreads), 0, st, qk, q_stride,
+                      kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.scale, a.softcap, a.temp,
+                      a.slopes, a.sink, a.window, a.keep_first, rm.slot, rm.pos, split_ws, arrived, out, out_b);
 }
 
 // a step of a few rows (decoding) splits every row's keys over CTAs; longer steps run the tiled kernel.
@@ -1189,8 +1229,8 @@ cudaError_t launch_residual_dyt(float* x, const float* y, const float* parts, co
 
 cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, void* out_bf16, int M, int D,
                               cudaStream_t st) {
-    dyt_gather_kernel<<<M, 256, 0, st>>>(x, rows, n.w, n.b, n.alpha, out, reinterpret_cast<__nv_bfloat16*>(out_bf16), D);
-    return cudaGetLastError();
+    return launch_pdl(dyt_gather_kernel, dim3(M), dim3(256), 0, st, x, rows, n.w, n.b, n.alpha, out,
+                      reinterpret_cast<__nv_bfloat16*>(out_bf16), D);
 }
 
 cudaError_t launch_argmax_rows(const float* logits, int M, int V, int* out, cudaStream_t st) {
