@@ -18,6 +18,10 @@ SURVEY.md 8(e)); `value` is the sum over ranks divided by the slowest rank's tim
                Python and cannot travel to the GPU box) timed on this box's host cores.
 
 `--impl reference` times that CPU port alone (rank 0 only).
+
+`--lm` leaves that workload aside and measures the decoder-only language-model path (Pubopel, random weights) at layer
+sizes of a real model: prefill and decode throughput through `CausalLM`, and its GEMM / attention kernels beside Dia's
+at equal size (one JSON line, metric `lm_layer_throughput`).
 """
 
 from __future__ import annotations
