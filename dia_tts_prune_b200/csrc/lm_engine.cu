@@ -15,7 +15,8 @@
 // A step of a few rows (decoding) runs the same arithmetic in fewer launches: norm + taps + tail in one, the output
 // projection with the norm and residual add in its epilogue, router + top experts in one, the gate inside the gate | up
 // product, and one kernel for the down products of a row's experts and the shared expert, their sum, the norm and the
-// residual add.
+// residual add.  When every sequence brings exactly one row (pure decoding), the kernels that finish a residual add
+// also write the next sublayer's norm + taps and move its tail.
 //
 // Products.  With float32 precision every product runs on the fp32 FMA kernels.  With bfloat16 precision a step of at
 // least kTensorRowsMin rows (a prompt portion) runs its products on the tensor cores (the tcgen05 kernel of
@@ -141,6 +142,13 @@ int check_layer(const lm_b200_model& m, const lm_b200_layer& l) {
     return LM_B200_OK;
 }
 
+// the input of sublayer `sub` of layer l as something the previous kernel's epilogue can produce (lm::TapOut)
+lm::TapOut tap_out(lm_b200_engine* e, const lm_b200_layer& l, int sub, const StepView& v) {
+    const lm_b200_norm& n = sub ? l.norm_ff_in : l.norm_mix_in;
+    const float* taps = sub ? l.tap_ff : l.tap_mix;
+    return lm::TapOut{n.w, n.b, n.alpha, taps, taps ? e->m.taps : 0, sub ? l.tail_ff : l.tail_mix, v.rm.slot, v.rm.pos, e->h};
+}
+
 // h = tapmix(norm(x)) and the tail of every scheduled sequence
 int norm_tapmix(lm_b200_engine* e, const lm_b200_layer& l, int sub, const float* x, const StepView& v, int M, int n_seq,
                 float* out, cudaStream_t st) {
@@ -161,7 +169,7 @@ int norm_tapmix(lm_b200_engine* e, const lm_b200_layer& l, int sub, const float*
 // y = mixer(h); with fuse_x, x += norm_mix_out(y) instead (in the output projection's epilogue where that runs on the
 // tensor cores).  hb: the bf16 copy of h when the caller has one.
 int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, const StepView& v, int M, float* y,
-          float* fuse_x, cudaStream_t st) {
+          float* fuse_x, const lm::TapOut& next, cudaStream_t st) {
     const int D = e->m.width, nq = l.heads * l.dim, nk = l.kv_heads * l.dim;
     const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
     if (tensor_path(e, M, nq + nk, D)) {
@@ -186,7 +194,7 @@ int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void*
         }
         LCK(dia::launch_gemm_tcgen05_bf16(e->attb, 1, l.w_o, D, y, M, D, nq, kPlain, nullptr, st));
     } else if (fuse_x && M <= lm::kRowsKernelMax) {
-        LCK(lm::launch_linear_rows_residual(e->att, nq, l.w_o, fuse_x, M, D, nq, N(l.norm_mix_out), st));
+        LCK(lm::launch_linear_rows_residual(e->att, nq, l.w_o, fuse_x, M, D, nq, N(l.norm_mix_out), next, st));
         return LM_B200_OK;
     } else {
         LCK(lm::launch_linear(e->att, nq, l.w_o, 0, y, D, M, D, nq, nullptr, st));
@@ -199,7 +207,7 @@ int mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void*
 // sum over the row's experts with the norm and the residual add, four launches.  Longer steps group the (row, expert)
 // assignments by expert for the tiled products.
 int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, float* x,
-                 const lm_b200_norm* norm, cudaStream_t st) {
+                 const lm_b200_norm* norm, const lm::TapOut& next, cudaStream_t st) {
     const int D = e->m.width, E = l.experts, top = l.top, F = l.expert_ff, Sf = l.shared_ff;
     const lm::NormW nrm = norm ? N(*norm) : lm::NormW{nullptr, nullptr, 0.f};
     if (M <= lm::kRowsKernelMax) {
@@ -208,7 +216,7 @@ int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
         LCK(lm::launch_gated_rows(h, D, l.w_gate_up, 2LL * F * D, e->mid, M * top, F, D, &rows, l.ws_gate_up, e->smid,
                                   Sf > 0 ? M : 0, Sf, st));
         LCK(lm::launch_down_combine_rows(e->mid, F, l.w_down, e->a_expert, top, Sf > 0 ? e->smid : nullptr, Sf, l.ws_down, x, M, D,
-                                         nrm, st));
+                                         nrm, next, st));
         return LM_B200_OK;
     }
     LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, E, M, E, D, nullptr, st));
@@ -363,18 +371,29 @@ int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_wan
     const StepView v = view(step, M, n_seq);
     const int D = e->m.width;
     LCK(lm::launch_embed(e->m.embed, v.token, e->x, M, e->m.vocab, D, st));
+    // Pure decoding (every scheduled sequence brings one row): the kernel that finishes a sublayer's residual add also
+    // writes the next sublayer's input and moves its tail, so the norm + taps launches between sublayers fall away.
+    const bool chain = M <= lm::kRowsKernelMax && n_seq == M;
+    const lm::TapOut none{};
+    bool h_ready = false;
     for (int i = 0; i < e->m.n_layer; ++i) {
         const lm_b200_layer& l = e->layers[i];
-        int rc = norm_tapmix(e, l, 0, e->x, v, M, n_seq, e->h, st);
+        const bool has_ff = l.ff == LM_B200_FF_ROUTED_EXPERTS, has_next = i + 1 < e->m.n_layer;
+        int rc = LM_B200_OK;
+        if (!h_ready) rc = norm_tapmix(e, l, 0, e->x, v, M, n_seq, e->h, st);
         if (rc) return rc;
         const void* hb = (e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin) ? e->hb : nullptr;
-        rc = mixer(e, l, e->h, hb, v, M, e->y, e->x, st);
+        const lm::TapOut after_mixer = !chain ? none : has_ff ? tap_out(e, l, 1, v) : has_next ? tap_out(e, e->layers[i + 1], 0, v) : none;
+        rc = mixer(e, l, e->h, hb, v, M, e->y, e->x, after_mixer, st);
         if (rc) return rc;
-        if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
-            rc = norm_tapmix(e, l, 1, e->x, v, M, n_seq, e->h, st);
+        h_ready = after_mixer.h != nullptr;
+        if (has_ff) {
+            if (!h_ready) rc = norm_tapmix(e, l, 1, e->x, v, M, n_seq, e->h, st);
             if (rc) return rc;
-            rc = feed_forward(e, l, e->h, hb, M, e->x, &l.norm_ff_out, st);
+            const lm::TapOut after_ff = (chain && has_next) ? tap_out(e, e->layers[i + 1], 0, v) : none;
+            rc = feed_forward(e, l, e->h, hb, M, e->x, &l.norm_ff_out, after_ff, st);
             if (rc) return rc;
+            h_ready = after_ff.h != nullptr;
         }
         if (layers_out) {
             if (cudaMemcpyAsync(layers_out + (size_t)i * M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, st) !=
@@ -466,7 +485,7 @@ int lm_b200_op_mixer(lm_b200_engine* e, int layer, const float* h, const int32_t
         return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
-    return mixer(e, e->layers[layer], h, nullptr, view(step, M, n_seq), M, y, nullptr, S(stream));
+    return mixer(e, e->layers[layer], h, nullptr, view(step, M, n_seq), M, y, nullptr, lm::TapOut{}, S(stream));
 }
 
 int lm_b200_op_attention(lm_b200_engine* e, int layer, float* qk, const int32_t* step, int M, int n_seq, float* out,
@@ -492,7 +511,7 @@ int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y,
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
-    return feed_forward(e, l, h, nullptr, M, y, nullptr, S(stream));                // no norm: the plain sum, written to y
+    return feed_forward(e, l, h, nullptr, M, y, nullptr, lm::TapOut{}, S(stream));                // no norm: the plain sum, written to y
 }
 
 int lm_b200_op_linear(const float* A, const void* W_bf16, float* Y, int M, int N, int K, void* stream) {

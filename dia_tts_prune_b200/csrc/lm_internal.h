@@ -22,6 +22,16 @@ struct AttnShape {
     float scale, softcap;
     const float* temp; const float* slopes; const float* sink;                  // per query head; each may be null
 };
+// After a kernel of a short step gave x[a][n] its new value, the NEXT sublayer's input for that element can follow in the
+// same thread when every scheduled sequence has exactly one row in the step: norm, taps over the sequence's tail, and
+// the tail update are all per (sequence, channel).  h == nullptr: nothing follows.
+struct TapOut {
+    const float* nw; const float* nb; float alpha;   // the next sublayer's input norm
+    const float* cw; int taps;                        // its taps [D][taps] (nullptr / 0: none)
+    float* tail;                                      // its tail [slots][taps - 1][D]
+    const int* row_slot; const int* row_pos;
+    float* h;                                         // [M][D]
+};
 struct GroupMap { int* a_row; float* a_scale; int* a_expert; int* n_slots; };   // expert-grouped assignment slots
 
 cudaError_t launch_embed(const void* table_bf16, const int* ids, float* out, int M, int V, int D, cudaStream_t st);
@@ -35,11 +45,12 @@ cudaError_t launch_linear(const float* A, int lda, const void* W_bf16, long long
 cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* cw, int taps, float* tail, const SeqMeta& sm,
                                   const RowMeta& rm, int n_seq, float* out, int D, cudaStream_t st);
 cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
-                                        cudaStream_t st);
+                                        const TapOut& next, cudaStream_t st);
 cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
                               int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st);
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
-                                     int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, cudaStream_t st);
+                                     int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, const TapOut& next,
+                                     cudaStream_t st);
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
                                int* slot_of, cudaStream_t st);
 cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,

@@ -324,12 +324,40 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ arow, const 
     return warp_sum(acc);
 }
 
+// The whole warp of output element (a, n): h[a][n] = tapmix(norm(x_new)) of the next sublayer and its tail update, for a
+// row that is its sequence's only row in the step.  Lane o fetches the input o positions back and its tap; the sum runs
+// in dyt_tapmix_seq_kernel's order, so both give the same bits.
+__device__ __forceinline__ void tap_out_warp(const TapOut& t, int a, int n, int D, float x_new, int lane) {
+    const float cur = dyt(x_new, t.alpha, t.nw[n], t.nb[n]);
+    const int taps = t.cw ? t.taps : 0, T1 = taps > 0 ? taps - 1 : 0;
+    float acc = cur;
+    if (taps > 0) acc = fmaf(t.cw[(size_t)n * taps + taps - 1], cur, acc);
+    if (T1 > 0) {
+        const int pos = t.row_pos[a];
+        float* tl = t.tail + (size_t)t.row_slot[a] * T1 * D + n;
+        float prev = 0.f, w = 0.f;
+        if (lane >= 1 && lane <= T1) {
+            prev = tl[(size_t)(T1 - lane) * D];
+            w = t.cw[(size_t)n * taps + taps - 1 - lane];
+        }
+        for (int o = 1; o <= T1; ++o) {
+            const float po = __shfl_sync(0xffffffffu, prev, o), wo = __shfl_sync(0xffffffffu, w, o);
+            if (pos - o >= 0) acc = fmaf(wo, po, acc);
+        }
+        __syncwarp();                                         // every lane has read its tail entry
+        if (lane >= 1 && lane <= T1 && T1 - lane - 1 >= 0) tl[(size_t)(T1 - lane - 1) * D] = prev;
+        if (lane == 0) tl[(size_t)(T1 - 1) * D] = cur;
+    }
+    if (lane == 0) t.h[(size_t)a * D + n] = acc;
+}
+
 // Y[a][n] = dot, or with res_x: res_x[a][n] += DynamicTanh(dot) (the residual stream takes the sublayer's output)
 __global__ void __launch_bounds__(256)
 linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
                    float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
                    const float* __restrict__ a_scale, const int* __restrict__ a_expert, const int* __restrict__ n_slots,
-                   float* __restrict__ res_x, const float* __restrict__ nw, const float* __restrict__ nb, float alpha) {
+                   float* __restrict__ res_x, const float* __restrict__ nw, const float* __restrict__ nb, float alpha,
+                   const TapOut next) {
     pdl_release();
     const bool mapped = a_row || a_scale || a_expert || n_slots;      // the maps are an earlier kernel's output
     if (mapped) pdl_wait();
@@ -344,9 +372,13 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     const float sc = a_scale ? a_scale[a] : 1.f;
     const __nv_bfloat16* wrow = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
     const float acc = warp_dot(A + (size_t)src * lda, wrow, K, lda, sc, lane, !mapped);
-    if (lane == 0) {
-        if (res_x) res_x[(size_t)a * ldy + n] += dyt(acc, alpha, nw[n], nb[n]);
-        else Y[(size_t)a * ldy + n] = acc;
+    if (res_x) {
+        const float x_new = res_x[(size_t)a * ldy + n] + dyt(acc, alpha, nw[n], nb[n]);
+        __syncwarp();                                         // all lanes have read the old value
+        if (lane == 0) res_x[(size_t)a * ldy + n] = x_new;
+        if (next.h) tap_out_warp(next, a, n, ldy, x_new, lane);
+    } else if (lane == 0) {
+        Y[(size_t)a * ldy + n] = acc;
     }
 }
 
@@ -393,7 +425,8 @@ gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __r
 __global__ void __launch_bounds__(256)
 down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat16* __restrict__ Wd, const int* __restrict__ a_expert,
                          int top, const float* __restrict__ smid, int Sf, const __nv_bfloat16* __restrict__ Wsd,
-                         float* __restrict__ x, int D, const float* __restrict__ nw, const float* __restrict__ nb, float alpha) {
+                         float* __restrict__ x, int D, const float* __restrict__ nw, const float* __restrict__ nb, float alpha,
+                         const TapOut next) {
     pdl_release();
     const int r = blockIdx.y;
     const int lane = threadIdx.x & 31;
@@ -406,9 +439,13 @@ down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat
         const int a = r * top + t;
         v += warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
     }
-    if (lane == 0) {
-        if (nw) x[(size_t)r * D + n] += dyt(v, alpha, nw[n], nb[n]);
-        else x[(size_t)r * D + n] = v;
+    if (nw) {
+        const float x_new = x[(size_t)r * D + n] + dyt(v, alpha, nw[n], nb[n]);
+        __syncwarp();                                         // all lanes have read the old value
+        if (lane == 0) x[(size_t)r * D + n] = x_new;
+        if (next.h) tap_out_warp(next, r, n, D, x_new, lane);
+    } else if (lane == 0) {
+        x[(size_t)r * D + n] = v;                             // no norm: the plain sum
     }
 }
 
@@ -1090,7 +1127,8 @@ cudaError_t launch_linear(const float* A, int lda, const void* W, long long w_ex
     // does not depend on how a prompt was cut)
     if (M <= kRowsKernelMax || (N <= kRowsKernelMaxOut && M <= 65535))
         return launch_pdl(linear_rows_kernel, dim3((N + 7) / 8, M), dim3(256), 0, st, A, lda, w, w_expert_stride, Y, ldy, M, N, K,
-                          a_row, a_scale, a_expert, n_slots, (float*)nullptr, (const float*)nullptr, (const float*)nullptr, 0.f);
+                          a_row, a_scale, a_expert, n_slots, (float*)nullptr, (const float*)nullptr, (const float*)nullptr, 0.f,
+                          TapOut{});
     else
         linear_tile_kernel<<<dim3((N + BN - 1) / BN, (M + BM - 1) / BM), 256, 0, st>>>(A, lda, w, w_expert_stride, Y, ldy, M, N,
                                                                                       K, a_row, a_scale, a_expert, n_slots);
@@ -1105,10 +1143,10 @@ cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* c
 }
 
 cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
-                                        cudaStream_t st) {
+                                        const TapOut& next, cudaStream_t st) {
     return launch_pdl(linear_rows_kernel, dim3((N + 7) / 8, M), dim3(256), 0, st, A, lda, reinterpret_cast<const __nv_bfloat16*>(W),
                       0LL, (float*)nullptr, N, M, N, K, (const int*)nullptr, (const float*)nullptr, (const int*)nullptr,
-                      (const int*)nullptr, x, n.w, n.b, n.alpha);
+                      (const int*)nullptr, x, n.w, n.b, n.alpha, next);
 }
 
 cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
@@ -1121,10 +1159,11 @@ cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long 
 }
 
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
-                                     int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, cudaStream_t st) {
+                                     int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, const TapOut& next,
+                                     cudaStream_t st) {
     return launch_pdl(down_combine_rows_kernel, dim3((D + 7) / 8, M), dim3(256), 0, st, mid, F,
                       reinterpret_cast<const __nv_bfloat16*>(Wd), a_expert, top, smid, Sf, reinterpret_cast<const __nv_bfloat16*>(Wsd), x,
-                      D, n.w, n.b, n.alpha);
+                      D, n.w, n.b, n.alpha, next);
 }
 
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,

@@ -450,6 +450,24 @@ def test_batched_decoding_with_bfloat16_products():
         mostly_close(lo.run_step(step), hi.run_step(step).cpu(), 4e-2, share=0.8)
 
 
+@pytest.mark.parametrize("make", [small_config, odd_config])
+def test_single_row_steps_chain_their_sublayers_to_the_same_bits(make):
+    """One row per sequence: the residual kernels also write the next sublayer's norm + taps and move its tail.  Two rows
+    of a sequence in one step take the separate kernels.  Both must give the same bits, tails included."""
+    cfg = make()
+    a, w = build(cfg, 46)
+    b, _ = build(cfg, 46)
+    toks = tokens(cfg, 41, 47)
+    for m in (a, b):
+        m.run_step([{"id": "s", "tokens": toks[:11], "want": []}])
+    for t in range(11, 41, 2):
+        one = torch.cat([a.run_step([{"id": "s", "tokens": [toks[t]], "want": [0]}]),
+                         a.run_step([{"id": "s", "tokens": [toks[t + 1]], "want": [0]}])])
+        two = b.run_step([{"id": "s", "tokens": toks[t:t + 2], "want": [0, 1]}])
+        assert torch.equal(one, two), t
+    close(one, O.forward(cfg, w, toks, dtype=torch.float64)[39:41])
+
+
 def test_replayed_step_graphs_give_the_same_bits_as_plain_launches():
     from dia_tts_prune_b200.lm_config import PubopelConfig
     from dia_tts_prune_b200.lm_engine import launch_count
