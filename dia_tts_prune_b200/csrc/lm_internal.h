@@ -6,7 +6,7 @@
 
 namespace lm {
 
-constexpr int kMaxTaps = 16;          // taps of the causal tap mix (the tail keeps taps - 1 rows per sequence)
+constexpr int kMaxTaps = 32;          // taps of the causal tap mix (the tail keeps taps - 1 rows per sequence)
 constexpr int kRowsKernelMax = 8;     // up to this many rows a linear layer runs one warp per output element
 constexpr int kRowsKernelMaxOut = 64; // ... and a linear layer of up to this many outputs at any number of rows
 constexpr int kTileRows = 64;         // row tile of the tiled linear kernel = padding of an expert group on that kernel

@@ -516,7 +516,7 @@ def drawn_config(seed):
                    "shared": r.choice([None, {"ff": 16}, {"ff": 33}])}
         layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
     return {"architecture": "Pubopel", "vocab": r.choice([50, 97, 128, 260]), "width": width,
-            "canon": {"taps": r.choice([1, 2, 3, 5, 16])}, "norm": {"eps": r.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
+            "canon": {"taps": 31 if seed % 8 == 7 else r.choice([1, 2, 3, 5, 16])}, "norm": {"eps": r.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
 
 
 @pytest.mark.parametrize("seed", range(8))
