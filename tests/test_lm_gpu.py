@@ -140,6 +140,25 @@ def test_attention_mixer_alone(make):
         close(got, ref, 1e-5)
 
 
+@pytest.mark.parametrize("dim", [136, 192, 200, 256])
+def test_attention_with_large_heads(dim):
+    """Head sizes beyond 128: the tiled kernel's wider variants and all eight values per lane of the split kernel."""
+    cfg = small_config(layers=[{"type": "attention", "mlp": None,
+                                "mixer": {"heads": 3, "kv_heads": 1, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                          "softcap": 25.0, "mask": {"size": 50, "keep_first": 3}}}], canon={"taps": 2})
+    model, w = build(cfg, 48)
+    T = 90
+    h = torch.randn(T, cfg["width"], generator=torch.Generator().manual_seed(dim))
+    p = {k[len("l0.mix."):]: v.double() for k, v in w.items() if k.startswith("l0.mix.")}
+    ref = O.sink_attention(h.double(), p, cfg["layers"][0]["mixer"], cfg["norm"]["eps"])
+    seq = model.state.open("t")
+    model.state.reserve(seq, T)
+    got = torch.cat([model.engine.op_mixer(0, h[:70].cuda(), [(seq, 70, 0)])] +
+                    [model.engine.op_mixer(0, h[t:t + 1].cuda(), [(seq, 1, t)]) for t in range(70, T)])
+    model.state.close("t")
+    close(got, ref, 1e-5)
+
+
 @pytest.mark.parametrize("make", [small_config, odd_config])
 @pytest.mark.parametrize("rows", [1, 3, 8, 40, 150])
 def test_routed_experts_alone(make, rows):
