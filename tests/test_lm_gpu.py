@@ -38,6 +38,11 @@ def odd_config():
     return cfg
 
 
+def unaligned_config():
+    """A width and a vocabulary that are multiples of nothing: no vector load and no tensor-core shape applies."""
+    return small_config(width=54, vocab=61)
+
+
 def build(cfg, seed=1, **kw):
     from dia_tts_prune_b200.lm_config import PubopelConfig
     from dia_tts_prune_b200.lm_model import CausalLM
@@ -191,7 +196,7 @@ def test_expert_score_scales_the_input_not_the_output():
 
 
 # ---- whole model: prompts, decoding, portions, batches -------------------------------------------------------------------
-@pytest.mark.parametrize("make", [small_config, odd_config])
+@pytest.mark.parametrize("make", [small_config, odd_config, unaligned_config])
 def test_whole_prompt_logits_and_layer_streams(make):
     cfg = make()
     model, w = build(cfg, 11)
@@ -204,7 +209,7 @@ def test_whole_prompt_logits_and_layer_streams(make):
         close(whole(model, "b", toks[:n]), ref[:n])
 
 
-@pytest.mark.parametrize("make", [small_config, odd_config])
+@pytest.mark.parametrize("make", [small_config, odd_config, unaligned_config])
 def test_prefill_then_long_token_by_token_decoding(make):
     cfg = make()
     model, w = build(cfg, 12)
@@ -423,7 +428,7 @@ def wide_config():
     return cfg
 
 
-@pytest.mark.parametrize("make", [wide_config, small_config, odd_config])
+@pytest.mark.parametrize("make", [wide_config, small_config, odd_config, unaligned_config])
 def test_bfloat16_products_stay_within_bfloat16_rounding_of_the_oracle(make):
     cfg = make()
     lo, hi, w = build_pair(cfg, 40)
@@ -432,7 +437,7 @@ def test_bfloat16_products_stay_within_bfloat16_rounding_of_the_oracle(make):
     exact, got = whole(hi, "a", toks), whole(lo, "a", toks)
     close(exact, ref)
     mostly_close(got, ref, 4e-2)
-    if make is not odd_config:                                  # (its sizes are off the tensor-core kernel's: same path)
+    if make in (wide_config, small_config):                     # (the others' sizes are off the tensor-core kernel's: same path)
         assert (got - exact).abs().max() > 1e-6                 # the portion did run on other arithmetic
     # portions (tensor cores from 32 rows on, FMA kernels below) and decoded tokens agree to the same rounding
     parts, at = [], 0
