@@ -11,8 +11,12 @@ from pathlib import Path
 
 from . import build as _build
 
-MIXER_SINK_ATTENTION = 1
-FF_NONE, FF_ROUTED_EXPERTS = 0, 1
+MIXER_SINK_ATTENTION, MIXER_TALK_ATTENTION, MIXER_HGRN2, MIXER_CHANNEL_DELTA = 1, 2, 3, 4
+FF_NONE, FF_ROUTED_EXPERTS, FF_DENSE = 0, 1, 2
+NORM_DYT, NORM_LAYER = 0, 1
+FORM_SEQUENTIAL, FORM_PARALLEL = 0, 1
+ACT_XIELU = 1
+ABI_VERSION = 2
 PRECISION_FP32, PRECISION_BF16 = 0, 1
 E_OK, E_INVAL, E_CUDA, E_NOMEM, E_UNSUPPORTED = 0, -1, -2, -3, -5
 
@@ -20,7 +24,7 @@ _vp, _i, _f = C.c_void_p, C.c_int32, C.c_float
 
 
 class Norm(C.Structure):
-    _fields_ = [("w", _vp), ("b", _vp), ("alpha", _f), ("reserved", _i)]
+    _fields_ = [("w", _vp), ("b", _vp), ("alpha", _f), ("kind", _i)]
 
 
 class Layer(C.Structure):
@@ -29,13 +33,19 @@ class Layer(C.Structure):
                 ("shared_ff", _i), ("norm_mix_in", Norm), ("norm_mix_out", Norm), ("norm_ff_in", Norm), ("norm_ff_out", Norm),
                 ("tap_mix", _vp), ("tap_ff", _vp), ("w_qk", _vp), ("q_norm", _vp), ("k_norm", _vp), ("temp", _vp),
                 ("slopes", _vp), ("sink", _vp), ("w_o", _vp), ("w_router", _vp), ("w_gate_up", _vp), ("w_down", _vp),
-                ("ws_gate_up", _vp), ("ws_down", _vp), ("k_pages", _vp), ("v_pages", _vp), ("tail_mix", _vp), ("tail_ff", _vp)]
+                ("ws_gate_up", _vp), ("ws_down", _vp), ("k_pages", _vp), ("v_pages", _vp), ("tail_mix", _vp), ("tail_ff", _vp),
+                # the parallel form
+                ("form", _i), ("vdim", _i), ("rot_dims", _i), ("conv_taps", _i), ("rank_a", _i), ("rank_g", _i), ("dense_ff", _i),
+                ("act", _i), ("act_p", _f), ("act_q", _f), ("unit_eps", _f), ("n_in", _i), ("k_out", _i), ("w_in", _vp),
+                ("in_bias", _vp), ("w_out", _vp), ("w_pre", _vp), ("rot_freq", _vp), ("talk", _vp), ("head_norm", _vp),
+                ("lower", _vp), ("conv_w", _vp), ("a_log", _vp), ("dt_bias", _vp), ("w_a2", _vp), ("w_g2", _vp),
+                ("rec_state", _vp), ("conv_tail", _vp)]
 
 
 class Model(C.Structure):
     _fields_ = [("n_layer", _i), ("width", _i), ("vocab", _i), ("taps", _i), ("page_size", _i), ("max_pages", _i),
                 ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("precision", _i), ("embed", _vp), ("head", _vp),
-                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("reserved", _i)]
+                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("logit_scale", _f)]
 
 
 _ci = C.c_int
@@ -81,7 +91,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if lib.lm_b200_abi_version() != 1:
+    if lib.lm_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("liblm_b200.so ABI version mismatch")
     _lib = lib
     return lib

@@ -18,6 +18,16 @@
 // residual add.  When every sequence brings exactly one row (pure decoding), the kernels that finish a residual add
 // also write the next sublayer's norm + taps and move its tail.
 //
+// A record of the parallel form (layer norm, one of the attention / recurrent mixers of lm_mixers.cu, a dense
+// feed-forward) runs
+//   [x = [x | x0] W_pre^T]                      pair_rows, linear            (x0: the embedding output; in front of a repeated block)
+//   h = layernorm(x)                            layernorm_rows
+//   proj = h W_in^T                             linear: every projection of the mixer and the feed-forward's up rows
+//   mixer on proj -> out[:, :mixer columns]     talk_prep + talk_attention | column_scan + head_norm_gate |
+//                                               delta_prep + conv_tail + column_scan + head_norm_gate
+//   out[:, mixer columns:] = act(proj up rows)  xielu_rows
+//   x += out W_out^T                            linear with the residual add (W_out = [W_o | W_down])
+//
 // Products.  With float32 precision every product runs on the fp32 FMA kernels.  With bfloat16 precision a step of at
 // least kTensorRowsMin rows (a prompt portion) runs its products on the tensor cores (the tcgen05 kernel of
 // gemm_tcgen05.cu, bf16 operands, fp32 accumulation in tensor memory): the norm / attention / gate kernels write the
@@ -85,6 +95,9 @@ struct lm_b200_engine {
     int *sel_e, *slot_of, *a_row, *a_expert, *n_slots;
     // bf16 operands of the tensor-core products (bfloat16 precision only)
     void *hb, *attb, *packb, *midb, *smidb, *hwb;
+    // the parallel layer form: embedding output, [x | x0], stacked projections, recurrence inputs, [mixer out | ff act]
+    float *x0, *cat, *proj, *rec, *outcat;
+    void *catb, *outcatb;
     float* split_ws;                             // partial results of the key splits of a few rows' attention
     unsigned* split_arrived;                     // ... and their arrival counters (zero between launches)
     // steps of a few rows are captured once per (rows, sequences, wanted) into a CUDA graph over these fixed buffers
@@ -127,7 +140,66 @@ StepView view(const int32_t* step, int M, int n_seq) {
     return v;
 }
 
+// columns of the stacked projections of a parallel record
+struct InCols { int q, k, v, gate, f, beta, a1, g1, up, n, mix_out; };
+InCols in_cols(const lm_b200_layer& l) {
+    InCols c{};
+    const int H = l.heads, G = l.kv_heads, d = l.dim, dv = l.vdim;
+    int at = 0;
+    if (l.mixer == LM_B200_MIXER_TALK_ATTENTION) {
+        c.q = at; at += H * d; c.k = at; at += G * d; c.v = at; at += G * dv; c.gate = at; at += H;
+    } else if (l.mixer == LM_B200_MIXER_HGRN2) {
+        c.q = at; at += H * d; c.f = at; at += H * d; c.v = at; at += H * dv;
+    } else {
+        c.q = at; at += G * d; c.k = at; at += G * d; c.v = at; at += H * dv; c.beta = at; at += H;
+        c.a1 = at; at += l.rank_a; c.g1 = at; at += l.rank_g;
+    }
+    c.up = at;
+    at += l.ff == LM_B200_FF_DENSE ? l.dense_ff : 0;
+    c.n = (at + 3) & ~3;
+    c.mix_out = H * dv;
+    return c;
+}
+// row of the recurrence inputs of a channel delta record: q | k | v | decay | gate | beta
+int rec_cols(const lm_b200_layer& l) {
+    return l.mixer == LM_B200_MIXER_CHANNEL_DELTA ? 2 * l.kv_heads * l.dim + 2 * l.heads * l.vdim + l.heads * l.dim + l.heads : 0;
+}
+lm::TalkShape talk_shape(const lm_b200_layer& l) {
+    return lm::TalkShape{l.heads, l.kv_heads, l.dim, l.vdim, l.rot_dims, l.scale, l.rot_freq, l.talk, l.sink};
+}
+
+int check_parallel_layer(const lm_b200_model& m, const lm_b200_layer& l) {
+    if (l.norm_mix_in.kind != LM_B200_NORM_LAYER || !l.norm_mix_in.w || !l.norm_mix_in.b) return LM_B200_EINVAL;
+    if (l.heads <= 0 || l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.vdim <= 0 || l.dim > 256 || l.vdim > 65536)
+        return LM_B200_EINVAL;
+    if (!l.w_in || !l.w_out) return LM_B200_EINVAL;
+    if (l.ff != LM_B200_FF_NONE && l.ff != LM_B200_FF_DENSE) return LM_B200_EUNSUPPORTED;
+    if (l.ff == LM_B200_FF_DENSE && (l.dense_ff <= 0 || l.act != LM_B200_ACT_XIELU)) return LM_B200_EINVAL;
+    const InCols c = in_cols(l);
+    if (l.n_in != c.n || l.k_out != c.mix_out + (l.ff == LM_B200_FF_DENSE ? l.dense_ff : 0)) return LM_B200_EINVAL;
+    switch (l.mixer) {
+        case LM_B200_MIXER_TALK_ATTENTION:
+            if (!l.q_norm || !l.k_norm || !l.k_pages || !l.v_pages || l.rot_dims < 0 || l.rot_dims % 2 || l.rot_dims > l.dim ||
+                (l.rot_dims > 0 && !l.rot_freq))
+                return LM_B200_EINVAL;
+            if (!lm::talk_attention_supported(talk_shape(l))) return LM_B200_EUNSUPPORTED;
+            return LM_B200_OK;
+        case LM_B200_MIXER_HGRN2:
+            if (l.heads != l.kv_heads || !l.head_norm || !l.rec_state) return LM_B200_EINVAL;
+            return LM_B200_OK;
+        case LM_B200_MIXER_CHANNEL_DELTA:
+            if (!l.head_norm || !l.rec_state || !l.conv_w || !l.a_log || !l.dt_bias || !l.w_a2 || !l.w_g2 || l.rank_a <= 0 ||
+                l.rank_g <= 0 || l.conv_taps < 1 || l.conv_taps > lm::kMaxTaps || (l.conv_taps > 1 && !l.conv_tail))
+                return LM_B200_EINVAL;
+            return LM_B200_OK;
+        default: return LM_B200_EUNSUPPORTED;
+    }
+    (void)m;
+}
+
 int check_layer(const lm_b200_model& m, const lm_b200_layer& l) {
+    if (l.form == LM_B200_FORM_PARALLEL) return check_parallel_layer(m, l);
+    if (l.form != LM_B200_FORM_SEQUENTIAL) return LM_B200_EUNSUPPORTED;
     if (l.mixer != LM_B200_MIXER_SINK_ATTENTION) return LM_B200_EUNSUPPORTED;
     if (l.heads <= 0 || l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.dim > 256) return LM_B200_EINVAL;
     if (!l.w_qk || !l.q_norm || !l.k_norm || !l.w_o || !l.k_pages || !l.v_pages) return LM_B200_EINVAL;
@@ -261,6 +333,99 @@ int feed_forward(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
     return LM_B200_OK;
 }
 
+// x = linear(A) or x += linear(A): the tensor-core kernel from kTensorRowsMin rows (its epilogue adds the residual),
+// the row kernel for a few rows (likewise), the tiled fp32 kernel with a separate add in between
+int product(lm_b200_engine* e, const float* A, const void* Ab, int lda, const void* W, float* out, int M, int N, int K,
+            bool add, cudaStream_t st) {
+    if (Ab && lda == K && tensor_path(e, M, N, K)) {
+        const dia::GemmEpilogue ep{add ? out : nullptr, nullptr, nullptr, 0.f};
+        LCK(dia::launch_gemm_tcgen05_bf16(Ab, 1, W, N, out, M, N, K, ep, nullptr, st));
+        return LM_B200_OK;
+    }
+    if (!add) {
+        LCK(lm::launch_linear(A, lda, W, 0, out, N, M, N, K, nullptr, st));
+        return LM_B200_OK;
+    }
+    if (M <= lm::kRowsKernelMax) {
+        LCK(lm::launch_linear_rows_residual(A, lda, W, out, M, N, K, lm::NormW{nullptr, nullptr, 0.f}, lm::TapOut{}, st));
+        return LM_B200_OK;
+    }
+    LCK(lm::launch_linear(A, lda, W, 0, e->y, N, M, N, K, nullptr, st));
+    LCK(lm::launch_add_rows(out, e->y, M, N, st));
+    return LM_B200_OK;
+}
+
+// One record of the parallel form.  only == 0: x += mixer(h) + ff(h) with h = norm(x) (after the input mix, if the record
+// has one).  only == 1 / 2: y = mixer(h_in) / ff(h_in) alone for a given h_in (operator boundaries).
+int parallel_layer(lm_b200_engine* e, const lm_b200_layer& l, const StepView& v, int M, int n_seq, int only, const float* h_in,
+                   float* y_out, cudaStream_t st) {
+    const int D = e->m.width;
+    const bool bf = e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin;
+    const InCols c = in_cols(l);
+    const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
+    const float* h = h_in;
+    const void* hb = nullptr;
+    if (only == 0) {
+        if (l.w_pre) {
+            LCK(lm::launch_pair_rows(e->x, e->x0, e->cat, bf ? e->catb : nullptr, M, D, st));
+            const int rc = product(e, e->cat, bf ? e->catb : nullptr, 2 * D, l.w_pre, e->x, M, D, 2 * D, false, st);
+            if (rc) return rc;
+        }
+        LCK(lm::launch_layernorm_rows(e->x, nullptr, l.norm_mix_in.w, l.norm_mix_in.b, e->m.eps, 1.f, e->h, bf ? e->hb : nullptr, M,
+                                      D, st));
+        h = e->h;
+        hb = bf ? e->hb : nullptr;
+    } else if (bf) {
+        LCK(lm::launch_pack_rows_bf16(h, e->hb, M, D, nullptr, st));
+        hb = e->hb;
+    }
+    int rc = product(e, h, hb, D, l.w_in, e->proj, M, c.n, D, false, st);
+    if (rc) return rc;
+    const int ko = l.k_out;
+    void* ob = bf ? e->outcatb : nullptr;
+    if (only != 0) {
+        if (cudaMemsetAsync(e->outcat, 0, (size_t)M * ko * 4, st) != cudaSuccess) return cuda_fail(cudaGetLastError());
+        if (ob && cudaMemsetAsync(ob, 0, (size_t)M * ko * 2, st) != cudaSuccess) return cuda_fail(cudaGetLastError());
+    }
+    if (only != 2) {
+        switch (l.mixer) {
+            case LM_B200_MIXER_TALK_ATTENTION: {
+                const lm::TalkShape a = talk_shape(l);
+                LCK(lm::launch_talk_prep(e->proj, c.n, l.in_bias, c.q, c.k, c.v, c.gate, a, l.q_norm, l.k_norm, e->m.eps, l.k_pages,
+                                         l.v_pages, pm, v.rm, M, st));
+                LCK(lm::launch_talk_attention(e->proj, c.n, c.q, c.gate, l.k_pages, l.v_pages, pm, a, v.rm, e->outcat, ko, ob,
+                                              e->split_ws, e->split_arrived, M, st));
+                break;
+            }
+            case LM_B200_MIXER_HGRN2: {
+                const lm::ScanInputs si{c.q, 0, c.f, c.v, 0, l.in_bias, l.lower};
+                LCK(lm::launch_column_scan(e->proj, c.n, si, false, l.heads, l.heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
+                                           e->outcat, ko, st));
+                LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, nullptr, 0, l.heads, l.vdim, e->m.eps, M, st));
+                break;
+            }
+            case LM_B200_MIXER_CHANNEL_DELTA: {
+                const lm::DeltaShape d{l.heads, l.kv_heads, l.dim, l.vdim, l.conv_taps, l.rank_a, l.rank_g, l.unit_eps, l.conv_w,
+                                       l.a_log, l.dt_bias, l.w_a2, l.w_g2};
+                const int ldr = rec_cols(l), C = 2 * l.kv_heads * l.dim + l.heads * l.vdim;
+                LCK(lm::launch_delta_prep(e->proj, c.n, c.beta, c.a1, c.g1, d, l.conv_tail, v.rm, e->rec, ldr, M, st));
+                LCK(lm::launch_conv_tail(e->proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
+                const int k0 = l.kv_heads * l.dim, v0 = 2 * k0, d0 = v0 + l.heads * l.vdim, g0 = d0 + l.heads * l.dim,
+                          b0 = g0 + l.heads * l.vdim;
+                const lm::ScanInputs si{0, k0, d0, v0, b0, nullptr, nullptr};
+                LCK(lm::launch_column_scan(e->rec, ldr, si, true, l.heads, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
+                                           e->outcat, ko, st));
+                LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, e->rec + g0, ldr, l.heads, l.vdim, e->m.eps, M, st));
+                break;
+            }
+            default: return LM_B200_EUNSUPPORTED;
+        }
+    }
+    if (only != 1 && l.ff == LM_B200_FF_DENSE)
+        LCK(lm::launch_xielu_rows(e->proj, c.n, c.up, l.act_p, l.act_q, e->outcat, ko, c.mix_out, ob, M, l.dense_ff, st));
+    return product(e, e->outcat, ob, ko, l.w_out, only == 0 ? e->x : y_out, M, D, ko, only == 0, st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -290,9 +455,20 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->device = device;
     const size_t R = (size_t)m.max_rows, D = (size_t)m.width;
     size_t qk = 0, att = 0, E = 1, top = 1, F = 1, Sf = 1, slots = 1;
+    size_t n_in = 0, k_out = 0, n_rec = 0, split_dim = 0;
+    bool pre = false;
     for (const lm_b200_layer& l : e->layers) {
+        if (l.form == LM_B200_FORM_PARALLEL) {
+            n_in = std::max(n_in, (size_t)l.n_in);
+            k_out = std::max(k_out, (size_t)l.k_out);
+            n_rec = std::max(n_rec, (size_t)rec_cols(l));
+            pre = pre || l.w_pre;
+            if (l.mixer == LM_B200_MIXER_TALK_ATTENTION) split_dim = std::max(split_dim, (size_t)l.heads * (l.vdim + 2));
+            continue;
+        }
         qk = std::max(qk, (size_t)(l.heads + l.kv_heads) * l.dim);
         att = std::max(att, (size_t)l.heads * l.dim);
+        split_dim = std::max(split_dim, (size_t)l.heads * (l.dim + 2));
         if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
             E = std::max(E, (size_t)l.experts);
             top = std::max(top, (size_t)l.top);
@@ -309,10 +485,9 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
                  o_slot_of = take(R * top * 4), o_a_row = take(slots * 4), o_a_scale = take(slots * 4),
                  o_a_expert = take(slots * 4), o_n_slots = take(4), o_gu = take(slots * 2 * F * 4), o_mid = take(slots * F * 4),
                  o_parts = take(slots * D * 4), o_sgu = take(R * 2 * Sf * 4), o_smid = take(R * Sf * 4), o_hw = take(R * D * 4);
-    size_t split = 0;
-    for (const lm_b200_layer& l : e->layers)
-        split = std::max(split, (size_t)lm::kAttnRowsKernelMax * l.heads * lm::kAttnSplitsMax * (l.dim + 2) * 4);
-    const size_t o_split = take(split);
+    const size_t o_x0 = take(pre ? R * D * 4 : 0), o_cat = take(pre ? R * 2 * D * 4 : 0), o_proj = take(R * n_in * 4),
+                 o_rec = take(R * n_rec * 4), o_outcat = take(R * k_out * 4);
+    const size_t o_split = take((size_t)lm::kAttnRowsKernelMax * lm::kAttnSplitsMax * split_dim * 4);
     size_t max_heads = 1;
     for (const lm_b200_layer& l : e->layers) max_heads = std::max(max_heads, (size_t)l.heads);
     const size_t arrived_bytes = (size_t)lm::kAttnRowsKernelMax * max_heads * 4, o_arrived = take(arrived_bytes);
@@ -320,6 +495,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     const bool tcb = m.precision == LM_B200_PRECISION_BF16;
     const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
                  o_midb = take(tcb ? slots * F * 2 : 0), o_smidb = take(tcb ? R * Sf * 2 : 0), o_hwb = take(tcb ? R * D * 2 : 0);
+    const size_t o_catb = take(tcb && pre ? R * 2 * D * 2 : 0), o_outcatb = take(tcb ? R * k_out * 2 : 0);
     if (cudaMalloc(&e->arena, off) != cudaSuccess) {
         (void)cudaGetLastError();
         delete e;
@@ -335,6 +511,8 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->smid = (float*)(b + o_smid); e->hw = (float*)(b + o_hw);
     e->hb = b + o_hb; e->attb = b + o_attb; e->packb = b + o_packb; e->midb = b + o_midb; e->smidb = b + o_smidb;
     e->hwb = b + o_hwb;
+    e->x0 = (float*)(b + o_x0); e->cat = (float*)(b + o_cat); e->proj = (float*)(b + o_proj); e->rec = (float*)(b + o_rec);
+    e->outcat = (float*)(b + o_outcat); e->catb = b + o_catb; e->outcatb = b + o_outcatb;
     e->split_ws = (float*)(b + o_split);
     e->split_arrived = (unsigned*)(b + o_arrived);
     if (cudaMemset(e->split_arrived, 0, arrived_bytes) != cudaSuccess) {
@@ -371,6 +549,10 @@ int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_wan
     const StepView v = view(step, M, n_seq);
     const int D = e->m.width;
     LCK(lm::launch_embed(e->m.embed, v.token, e->x, M, e->m.vocab, D, st));
+    bool keep_x0 = false;
+    for (const lm_b200_layer& l : e->layers) keep_x0 = keep_x0 || (l.form == LM_B200_FORM_PARALLEL && l.w_pre);
+    if (keep_x0 && cudaMemcpyAsync(e->x0, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return cuda_fail(cudaGetLastError());
     // Pure decoding (every scheduled sequence brings one row): the kernel that finishes a sublayer's residual add also
     // writes the next sublayer's input and moves its tail, so the norm + taps launches between sublayers fall away.
     const bool chain = M <= lm::kRowsKernelMax && n_seq == M;
@@ -378,7 +560,16 @@ int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_wan
     bool h_ready = false;
     for (int i = 0; i < e->m.n_layer; ++i) {
         const lm_b200_layer& l = e->layers[i];
-        const bool has_ff = l.ff == LM_B200_FF_ROUTED_EXPERTS, has_next = i + 1 < e->m.n_layer;
+        if (l.form == LM_B200_FORM_PARALLEL) {
+            const int prc = parallel_layer(e, l, v, M, n_seq, 0, nullptr, nullptr, st);
+            if (prc) return prc;
+            h_ready = false;
+            if (layers_out && cudaMemcpyAsync(layers_out + (size_t)i * M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice,
+                                              st) != cudaSuccess)
+                return cuda_fail(cudaGetLastError());
+            continue;
+        }
+        const bool has_ff = l.ff == LM_B200_FF_ROUTED_EXPERTS, has_next = i + 1 < e->m.n_layer && e->layers[i + 1].form == LM_B200_FORM_SEQUENTIAL;
         int rc = LM_B200_OK;
         if (!h_ready) rc = norm_tapmix(e, l, 0, e->x, v, M, n_seq, e->h, st);
         if (rc) return rc;
@@ -406,7 +597,11 @@ int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_wan
         // sequences) the tensor-core kernel reads it once for all rows, where the row kernel reads it once per row
         const bool tc = e->m.precision == LM_B200_PRECISION_BF16 && n_want >= kHeadTensorRowsMin &&
                         dia::gemm_tcgen05_shape_ok(n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
-        LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
+        if (e->m.final_norm.kind == LM_B200_NORM_LAYER)
+            LCK(lm::launch_layernorm_rows(e->x, v.want, e->m.final_norm.w, e->m.final_norm.b, e->m.eps,
+                                          e->m.logit_scale != 0.f ? e->m.logit_scale : 1.f, e->hw, tc ? e->hwb : nullptr, n_want, D, st));
+        else
+            LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
         if (tc)
             LCK(dia::launch_gemm_tcgen05_bf16(e->hwb, 1, e->m.head, e->m.vocab, logits_out, n_want, e->m.vocab, D, kPlain, nullptr, st));
         else
@@ -476,6 +671,7 @@ int lm_b200_op_norm_tapmix(lm_b200_engine* e, int layer, int sub, const float* x
         return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
+    if (e->layers[layer].form != LM_B200_FORM_SEQUENTIAL) return LM_B200_EUNSUPPORTED;
     return norm_tapmix(e, e->layers[layer], sub, x, view(step, M, n_seq), M, n_seq, out, S(stream));
 }
 
@@ -485,6 +681,8 @@ int lm_b200_op_mixer(lm_b200_engine* e, int layer, const float* h, const int32_t
         return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
+    if (e->layers[layer].form == LM_B200_FORM_PARALLEL)
+        return parallel_layer(e, e->layers[layer], view(step, M, n_seq), M, n_seq, 1, h, y, S(stream));
     return mixer(e, e->layers[layer], h, nullptr, view(step, M, n_seq), M, y, nullptr, lm::TapOut{}, S(stream));
 }
 
@@ -495,6 +693,7 @@ int lm_b200_op_attention(lm_b200_engine* e, int layer, float* qk, const int32_t*
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;
     const lm_b200_layer& l = e->layers[layer];
+    if (l.form != LM_B200_FORM_SEQUENTIAL) return LM_B200_EUNSUPPORTED;
     const StepView v = view(step, M, n_seq);
     const int nq = l.heads * l.dim, nk = l.kv_heads * l.dim;
     const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
@@ -508,6 +707,12 @@ int lm_b200_op_attention(lm_b200_engine* e, int layer, float* qk, const int32_t*
 int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y, void* stream) {
     if (!e || layer < 0 || layer >= e->m.n_layer || !h || !y || M <= 0 || M > e->m.max_rows) return LM_B200_EINVAL;
     const lm_b200_layer& l = e->layers[layer];
+    if (l.form == LM_B200_FORM_PARALLEL) {
+        if (l.ff != LM_B200_FF_DENSE) return LM_B200_EINVAL;
+        Guard g(e->device);
+        if (!g.ok) return LM_B200_ECUDA;
+        return parallel_layer(e, l, StepView{}, M, 0, 2, h, y, S(stream));
+    }
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;
     Guard g(e->device);
     if (!g.ok) return LM_B200_ECUDA;

@@ -1,4 +1,4 @@
-// lm_internal.h - shared declarations of the language-model path (lm_kernels.cu, lm_engine.cu).
+// lm_internal.h - shared declarations of the language-model path (lm_kernels.cu, lm_mixers.cu, lm_engine.cu).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -69,5 +69,43 @@ cudaError_t launch_residual_dyt(float* x, const float* y, const float* parts, co
 cudaError_t launch_dyt_gather(const float* x, const int* rows, const NormW& n, float* out, void* out_bf16, int M, int D,
                               cudaStream_t st);
 cudaError_t launch_argmax_rows(const float* logits, int M, int V, int* out, cudaStream_t st);
+
+// ---- the parallel layer form (lm_mixers.cu) ----
+struct TalkShape {
+    int heads, kv_heads, dim, vdim, rot_dims;
+    float scale;
+    const float* rot_freq;                                                      // [rot_dims / 2]
+    const float* talk; const float* sink;                                       // [heads][heads], [heads]; each may be null
+};
+struct DeltaShape {
+    int heads, kv_heads, dim, vdim, taps, rank_a, rank_g;
+    float unit_eps;
+    const float* conv_w; const float* a_log; const float* dt_bias; const float* w_a2; const float* w_g2;
+};
+// columns of the recurrence's inputs in their row; in_bias / lower transform the gate-tied form's inputs (may be null)
+struct ScanInputs { int q_off, k_off, a_off, v_off, beta_off; const float* in_bias; const float* lower; };
+
+cudaError_t launch_layernorm_rows(const float* x, const int* rows, const float* w, const float* b, float eps, float out_scale,
+                                  float* out, void* out_bf16, int M, int D, cudaStream_t st);
+cudaError_t launch_pair_rows(const float* x, const float* x0, float* cat, void* cat_bf16, int M, int D, cudaStream_t st);
+cudaError_t launch_add_rows(float* x, const float* y, int M, int D, cudaStream_t st);
+cudaError_t launch_xielu_rows(const float* proj, int ld, int off, float ap, float an, float* out, int ldo, int out_off,
+                              void* out_bf16, int M, int F, cudaStream_t st);
+cudaError_t launch_talk_prep(float* proj, int ld, const float* bias, int q_off, int k_off, int v_off, int gate_off,
+                             const TalkShape& a, const float* qw, const float* kw, float eps, float* kcache, float* vcache,
+                             const PageMap& pm, const RowMeta& rm, int M, cudaStream_t st);
+bool talk_attention_supported(const TalkShape& a);
+cudaError_t launch_talk_attention(const float* proj, int ld, int q_off, int gate_off, const float* kcache, const float* vcache,
+                                  const PageMap& pm, const TalkShape& a, const RowMeta& rm, float* out, int ldo, void* out_bf16,
+                                  float* split_ws, unsigned* arrived, int M, cudaStream_t st);
+cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, int a1_off, int g1_off, const DeltaShape& d,
+                              const float* tail, const RowMeta& rm, float* rec, int ldr, int M, cudaStream_t st);
+cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* tail, const SeqMeta& sm, int n_seq,
+                             cudaStream_t st);
+cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
+                               float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
+                               cudaStream_t st);
+cudaError_t launch_head_norm_gate(float* o, int ldo, void* o_bf16, const float* w, const float* gate, int ldg, int H, int vdim,
+                                  float eps, int M, cudaStream_t st);
 
 }  // namespace lm

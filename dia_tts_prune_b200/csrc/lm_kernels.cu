@@ -40,45 +40,11 @@
 #include <math_constants.h>
 #include <stdint.h>
 
+#include "lm_device.cuh"
 #include "lm_internal.h"
 
 namespace lm {
 
-namespace {
-
-__device__ __forceinline__ float bf(const __nv_bfloat16 v) { return __bfloat162float(v); }
-
-__device__ __forceinline__ float dyt(float x, float alpha, float w, float b) { return fmaf(tanhf(alpha * x), w, b); }
-
-// Programmatic dependent launch: a kernel of a short step lets the next one start as soon as it runs itself
-// (pdl_release) and reads what earlier kernels wrote - or writes anything - only after pdl_wait.  Before the wait a
-// kernel may fetch weights, which no kernel writes.  Launched without the attribute both are no-ops.
-__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
-// fixed-tree block reductions (red: one float per warp); every thread gets the result
-__device__ __forceinline__ float block_sum(float v, float* red) {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    v = warp_sum(v);
-    __syncthreads();
-    if (lane == 0) red[w] = v;
-    __syncthreads();
-    float t = 0.f;
-    for (int i = 0; i < nw; ++i) t += red[i];
-    return t;
-}
-}  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void embed_rows_bf16_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
@@ -351,7 +317,8 @@ __device__ __forceinline__ void tap_out_warp(const TapOut& t, int a, int n, int 
     if (lane == 0) t.h[(size_t)a * D + n] = acc;
 }
 
-// Y[a][n] = dot, or with res_x: res_x[a][n] += DynamicTanh(dot) (the residual stream takes the sublayer's output)
+// Y[a][n] = dot, or with res_x: res_x[a][n] += DynamicTanh(dot), += dot without a norm (the residual stream takes the
+// sublayer's output)
 __global__ void __launch_bounds__(256)
 linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
                    float* __restrict__ Y, int ldy, int M, int N, int K, const int* __restrict__ a_row,
@@ -373,7 +340,7 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     const __nv_bfloat16* wrow = W + (a_expert ? (size_t)a_expert[a] * (size_t)w_expert_stride : 0) + (size_t)n * K;
     const float acc = warp_dot(A + (size_t)src * lda, wrow, K, lda, sc, lane, !mapped);
     if (res_x) {
-        const float x_new = res_x[(size_t)a * ldy + n] + dyt(acc, alpha, nw[n], nb[n]);
+        const float x_new = res_x[(size_t)a * ldy + n] + (nw ? dyt(acc, alpha, nw[n], nb[n]) : acc);
         __syncwarp();                                         // all lanes have read the old value
         if (lane == 0) res_x[(size_t)a * ldy + n] = x_new;
         if (next.h) tap_out_warp(next, a, n, ldy, x_new, lane);
@@ -1080,22 +1047,6 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int*
 }
 
 // ---- launchers --------------------------------------------------------------------------------------------------------
-// the kernels of a short step are launched with programmatic stream serialization (see pdl_release / pdl_wait)
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
 cudaError_t launch_embed(const void* table, const int* ids, float* out, int M, int V, int D, cudaStream_t st) {
     return launch_pdl(embed_rows_bf16_kernel, dim3(M), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(table), ids, out, V, D);
 }

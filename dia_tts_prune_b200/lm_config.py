@@ -1,4 +1,4 @@
-"""Configuration schema of the Pubopel decoder-only language model (``config.json`` of a model folder).
+"""Configuration schemas of the decoder-only language models (``config.json`` of a model folder): Pubopel and Kupelix.
 
 Every size and every per-model constant comes from the file.  Optional entries that are absent switch their
 mechanism off: no ``mask`` is full causal attention, no ``softcap`` leaves scores uncapped, ``mlp: null`` is a layer
@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import json
 from pathlib import Path
-from typing import Literal, Optional
+from typing import Annotated, Literal, Optional, Union
 
 from pydantic import BaseModel, Field
 
@@ -80,3 +80,120 @@ class PubopelConfig(BaseModel, frozen=True):
                 raise ValueError(f"layer {i}: the values are the projected keys, so vdim ({m.vdim}) must equal dim ({m.dim})")
             if layer.mlp is not None and layer.mlp.router.top > layer.mlp.router.experts:
                 raise ValueError(f"layer {i}: top ({layer.mlp.router.top}) exceeds experts ({layer.mlp.router.experts})")
+
+
+# ---- Kupelix: parallel layers (one layer norm feeds mixer and feed-forward), three mixers, an optional repeated block ----
+class RotScalingConfig(BaseModel, frozen=True):
+    factor: float = Field(gt=0.0)
+    low: float
+    high: float
+    original: float = Field(gt=0.0)
+
+
+class RotConfig(BaseModel, frozen=True):
+    base: float = Field(gt=0.0)
+    dims: int = Field(ge=0)                      # leading channels of every head that turn with the position
+    scaling: Optional[RotScalingConfig] = None
+
+
+class TalkAttentionMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    kv_heads: Optional[int] = Field(default=None, gt=0)
+    dim: int = Field(gt=0)
+    vdim: int = Field(gt=0)
+    scale: float
+    rot: Optional[RotConfig] = None
+
+
+class Hgrn2MixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    dim: int = Field(gt=0)
+    vdim: int = Field(gt=0)
+
+
+class ChannelDeltaMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    kv_heads: Optional[int] = Field(default=None, gt=0)
+    dim: int = Field(gt=0)
+    vdim: int = Field(gt=0)
+    conv: int = Field(ge=1)                      # taps of the short convolutions of q, k, v
+
+
+class DenseMlpConfig(BaseModel, frozen=True):
+    kind: Literal["dense"] = "dense"
+    ff: int = Field(gt=0)
+
+
+class KupelixAttentionLayer(BaseModel, frozen=True):
+    type: Literal["attention"]
+    mixer: TalkAttentionMixerConfig
+    mlp: Optional[DenseMlpConfig] = None
+
+
+class KupelixHgrn2Layer(BaseModel, frozen=True):
+    type: Literal["hgrn2"]
+    mixer: Hgrn2MixerConfig
+    mlp: Optional[DenseMlpConfig] = None
+
+
+class KupelixDeltaLayer(BaseModel, frozen=True):
+    type: Literal["channel_delta"]
+    mixer: ChannelDeltaMixerConfig
+    mlp: Optional[DenseMlpConfig] = None
+
+
+KupelixLayer = Annotated[Union[KupelixAttentionLayer, KupelixHgrn2Layer, KupelixDeltaLayer], Field(discriminator="type")]
+
+
+class LoopConfig(BaseModel, frozen=True):
+    start: int = Field(ge=0)                     # layers start .. stop-1 run `times` times in a row with the same weights
+    stop: int = Field(ge=0)
+    times: int = Field(ge=1)
+
+
+class KupelixConfig(BaseModel, frozen=True):
+    architecture: Literal["Kupelix"] = "Kupelix"
+    vocab: int = Field(gt=0)
+    width: int = Field(gt=0)
+    layers: list[KupelixLayer] = Field(min_length=1)
+    loop: Optional[LoopConfig] = None
+    norm: NormConfig
+    logit_scale: float = 1.0
+
+    @classmethod
+    def load(cls, path: str | Path) -> "KupelixConfig":
+        return cls.model_validate(json.loads(Path(path).read_text(encoding="utf-8")))
+
+    def check(self) -> None:
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            g = getattr(m, "kv_heads", None) or m.heads
+            if m.heads % g:
+                raise ValueError(f"layer {i}: heads ({m.heads}) must be a multiple of kv_heads ({g})")
+            rot = getattr(m, "rot", None)
+            if rot is not None and (rot.dims % 2 or rot.dims > m.dim):
+                raise ValueError(f"layer {i}: rot.dims ({rot.dims}) must be even and at most dim ({m.dim})")
+        if self.loop is not None and not (0 <= self.loop.start < self.loop.stop <= len(self.layers)):
+            raise ValueError("loop: start < stop <= number of layers is required")
+
+    def runs(self) -> list[tuple[int, bool]]:
+        """(layer index, whether a pass of the repeated block starts here) in execution order."""
+        n = len(self.layers)
+        if self.loop is None:
+            return [(i, False) for i in range(n)]
+        a, b = self.loop.start, self.loop.stop
+        out = [(i, False) for i in range(a)]
+        for _ in range(self.loop.times):
+            out += [(i, i == a) for i in range(a, b)]
+        return out + [(i, False) for i in range(b, n)]
+
+
+CONFIGS = {"pubopel": PubopelConfig, "kupelix": KupelixConfig}
+
+
+def load_config(raw: dict):
+    """The configuration object of a language model's ``config.json`` dictionary, by its ``architecture``."""
+    name = str(raw.get("architecture", "")).lower()
+    if name not in CONFIGS:
+        raise NotImplementedError(f"no language-model configuration for architecture {raw.get('architecture')!r}")
+    return CONFIGS[name].model_validate(raw)

@@ -13,7 +13,7 @@ import numpy as np
 import torch
 
 from . import _lm_lib
-from .lm_layers import DynamicTanh, MixLayer
+from .lm_layers import DynamicTanh, LayerNorm, MixLayer
 from .lm_state import PagedState, Sequence
 
 
@@ -26,9 +26,11 @@ def launch_count() -> int:
 
 
 class LMEngine:
-    def __init__(self, layers: list[MixLayer], embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh, *,
+    def __init__(self, layers: list, embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh | LayerNorm, *,
                  width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024,
-                 precision: str = "bfloat16", step_graphs: bool = True):
+                 precision: str = "bfloat16", step_graphs: bool = True, logit_scale: float = 1.0):
+        """``layers``: the layer records in execution order (a layer that runs twice per token appears twice, each time
+        with the state record of its own index)."""
         if not torch.cuda.is_available():
             raise RuntimeError("the language-model path needs a CUDA device (sm_100a); there is no CPU fallback")
         self.lib = _lm_lib.load()
@@ -54,9 +56,10 @@ class LMEngine:
         final_norm.fill(m.final_norm)
         m.page_table = state.page_table.data_ptr()
         m.step_graphs = 1 if step_graphs else 0
+        m.logit_scale = float(logit_scale)
         recs = (_lm_lib.Layer * len(layers))()
         for i, layer in enumerate(layers):
-            layer.fill(recs[i], state.k_pages[i], state.v_pages[i], state.tails[i][0], state.tails[i][1])
+            layer.fill(recs[i], state.record_state(i))
         self._h = C.c_void_p()
         _lm_lib.check(self.lib.lm_b200_engine_create(C.byref(m), recs, self.device.index, C.byref(self._h)), "engine_create")
         self.workspace_bytes = int(self.lib.lm_b200_engine_workspace_bytes(self._h))

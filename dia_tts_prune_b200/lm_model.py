@@ -18,9 +18,10 @@ from pathlib import Path
 import torch
 
 from .checkpoint import load_safetensors
-from .lm_config import PubopelConfig
+from .lm_config import KupelixConfig, PubopelConfig, load_config
 from .lm_engine import LMEngine
-from .lm_layers import DynamicTanh, MixLayer, RoutedExperts, SinkAttention, TapMix
+from .lm_layers import (ChannelDelta, DenseXielu, DynamicTanh, Hgrn2, LayerNorm, LayerRun, MixLayer, ParallelLayer, RoutedExperts,
+                        SinkAttention, TalkingAttention, TapMix, rotary_angles)
 from .lm_state import OutOfPages, PagedState, Sequence
 
 
@@ -55,6 +56,36 @@ def build_pubopel_layers(cfg: PubopelConfig, w: dict[str, torch.Tensor], device)
             n2, n2b, t2 = norm(p + "norm2"), norm(p + "norm2b"), TapMix(w[p + "canon2"], device)
         layers.append(MixLayer(attn, norm(p + "norm1"), norm(p + "norm1b"), TapMix(w[p + "canon1"], device), ff, n2, n2b, t2))
     return layers, norm("final.norm")
+
+
+def build_kupelix_layers(cfg: KupelixConfig, w: dict[str, torch.Tensor], device) -> tuple[list[LayerRun], LayerNorm]:
+    """The layer records of a Kupelix checkpoint in execution order (tensor names ``l<i>.norm1``, ``l<i>.mix.*``,
+    ``l<i>.mlp.*``, ``loop.in``): every layer is built once, and a layer inside the repeated block appears once per pass,
+    the first layer of each pass with the input mix in front."""
+    built = []
+    for i, lc in enumerate(cfg.layers):
+        p, m = f"l{i}.mix.", lc.mixer
+        t = lambda name: w[p + name]                             # noqa: E731
+        if lc.type == "attention":
+            rot = rotary_angles(m.rot.base, m.rot.dims, m.rot.scaling) if m.rot is not None and m.rot.dims > 0 else None
+            mixer = TalkingAttention(t("q"), t("k"), t("v"), t("o"), t("q.norm"), t("k.norm"), heads=m.heads,
+                                     kv_heads=m.kv_heads or m.heads, dim=m.dim, vdim=m.vdim, scale=m.scale, b_q=t("q.b"),
+                                     b_k=t("k.b"), b_v=t("v.b"), w_gate=t("g"), talk=t("talk"), sink=t("sink"), rot_angles=rot,
+                                     device=device)
+        elif lc.type == "hgrn2":
+            mixer = Hgrn2(t("q"), t("f"), t("v"), t("o"), t("norm"), heads=m.heads, dim=m.dim, vdim=m.vdim, b_f=t("f.b"),
+                          lower=t("lower"), device=device)
+        else:
+            mixer = ChannelDelta(t("q"), t("k"), t("v"), t("b"), t("a1"), t("a2"), t("g1"), t("g2"), t("o"), t("q.conv"),
+                                 t("k.conv"), t("v.conv"), t("A_log"), t("dt_bias"), t("norm"), heads=m.heads,
+                                 kv_heads=m.kv_heads or m.heads, dim=m.dim, vdim=m.vdim, device=device)
+        ff = None
+        if lc.mlp is not None:
+            ff = DenseXielu(w[f"l{i}.mlp.up"], w[f"l{i}.mlp.down"], w[f"l{i}.mlp.act"])
+        built.append(ParallelLayer(LayerNorm(w[f"l{i}.norm1"], w[f"l{i}.norm1.b"], device), mixer, ff, device))
+    pre = w["loop.in"] if cfg.loop is not None else None
+    runs = [LayerRun(built[i], pre if starts else None, device) for i, starts in cfg.runs()]
+    return runs, LayerNorm(w["final.norm"], w["final.norm.b"], device)
 
 
 @dataclass
@@ -143,7 +174,7 @@ class Scheduler:
 
 
 class CausalLM:
-    def __init__(self, cfg: PubopelConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
+    def __init__(self, cfg: PubopelConfig | KupelixConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
                  max_tokens: int = 4096, max_sequences: int = 8, page_size: int = 16, max_rows: int = 1024,
                  max_sequence_tokens: int | None = None, step_graphs: bool = True):
         if dtype not in ("bfloat16", "float32"):
@@ -153,22 +184,27 @@ class CausalLM:
         cfg.check()
         self.config, self.dtype = cfg, dtype
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.layers, final_norm = build_pubopel_layers(cfg, weights, self.device)
-        self.state = PagedState([(lc.mixer.kv_heads, lc.mixer.dim) for lc in cfg.layers], cfg.width, cfg.canon.taps,
-                                max_tokens, self.device, page_size=page_size, max_sequences=max_sequences,
-                                max_sequence_tokens=max_sequence_tokens)
+        # a design is its layer records (in execution order), its final norm and the constants around them
+        if isinstance(cfg, KupelixConfig):
+            self.layers, final_norm = build_kupelix_layers(cfg, weights, self.device)
+            taps, logit_scale = 0, cfg.logit_scale
+        else:
+            self.layers, final_norm = build_pubopel_layers(cfg, weights, self.device)
+            taps, logit_scale = cfg.canon.taps, 1.0
+        self.state = PagedState([layer.state_spec() for layer in self.layers], cfg.width, taps, max_tokens, self.device,
+                                page_size=page_size, max_sequences=max_sequences, max_sequence_tokens=max_sequence_tokens)
         # float32: every product is fp32 arithmetic on the stored (bfloat16) weights.  bfloat16: the products of prompt
         # portions run on the tensor cores with bfloat16 operands and fp32 accumulation.  Norms, scores, the router, the
-        # pages and the residual stream are float32 in both.
+        # pages, recurrent states and the residual stream are float32 in both.
         self.engine = LMEngine(self.layers, weights["embed"], weights["head"], final_norm, width=cfg.width, vocab=cfg.vocab,
-                               taps=cfg.canon.taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype,
-                               step_graphs=step_graphs)
+                               taps=taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype,
+                               step_graphs=step_graphs, logit_scale=logit_scale)
         self._draws = 0
 
     @classmethod
     def from_pretrained(cls, folder: str | Path, dtype: str = "bfloat16", device=None, **kw) -> "CausalLM":
         folder = Path(folder)
-        cfg = PubopelConfig.model_validate(json.loads((folder / "config.json").read_text(encoding="utf-8")))
+        cfg = load_config(json.loads((folder / "config.json").read_text(encoding="utf-8")))
         return cls(cfg, load_safetensors(folder / "model.safetensors"), dtype=dtype, device=device, **kw)
 
     # ---- teacher-forced stepping (trace replay, scoring) -------------------------------------------------------

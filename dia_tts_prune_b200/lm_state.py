@@ -1,10 +1,14 @@
-"""Sequence state of the language-model path: paged K/V storage, per-sequence slots and short-convolution tails.
+"""Sequence state of the language-model path: paged K/V storage, per-sequence slots, short-convolution tails and
+recurrent states.
 
 Same role as ``state.py`` has for Dia (``KVCache`` / ``DecoderInferenceState``), but for any number of concurrent
-sequences of unknown final length: a sequence owns a *slot* (a row of the page table and of every layer's tail
-buffers) and a list of fixed-size *pages* of the shared K/V pool, taken when its length crosses a page border and
-given back when it ends.  Slots and pages are recycled last-freed-first.  The kernels read the device copy of the
-page table; the bookkeeping is host-side and never reads a device tensor.
+sequences of unknown final length: a sequence owns a *slot* (a row of the page table, of every layer's tail buffers
+and of every recurrent layer's state) and a list of fixed-size *pages* of the shared K/V pool, taken when its length
+crosses a page border and given back when it ends.  Slots and pages are recycled last-freed-first; nothing is cleared
+on reuse, because the kernels take a sequence's state as zero when its first row of a step is position 0.  What a layer
+record keeps is described by a :class:`StateSpec`; a layer that runs several times per token has one record, and so
+one state, per run.  The kernels read the device copy of the page table; the bookkeeping is host-side and never reads
+a device tensor.
 """
 
 from __future__ import annotations
@@ -12,6 +16,15 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 import torch
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """What one layer record keeps per sequence (every part optional)."""
+    kv: tuple[int, int, int] | None = None          # (kv_heads, key size, value size): paged keys and values
+    tap_tails: int = 0                              # [taps - 1][width] tails of tap-mix sublayers
+    recurrent: tuple[int, int, int] | None = None   # (heads, value size, key size): fp32 matrix state per slot
+    conv: tuple[int, int] | None = None             # (taps, channels): the last taps - 1 inputs of a short convolution
 
 
 class OutOfPages(RuntimeError):
@@ -27,11 +40,21 @@ class Sequence:
     pages: list[int] = field(default_factory=list)
 
 
+@dataclass
+class RecordState:
+    k_pages: torch.Tensor | None
+    v_pages: torch.Tensor | None
+    tails: tuple
+    rec_state: torch.Tensor | None
+    conv_tail: torch.Tensor | None
+
+
 class PagedState:
-    def __init__(self, layers: list[tuple[int, int]], width: int, taps: int, max_tokens: int, device: torch.device,
+    def __init__(self, layers: list, width: int, taps: int, max_tokens: int, device: torch.device,
                  page_size: int = 16, max_sequences: int = 8, max_sequence_tokens: int | None = None):
-        """``layers``: (kv_heads, dim) of every layer.  ``max_tokens``: the most tokens all live sequences hold at one
-        time; the pool gets that many tokens' worth of pages plus one partly filled page per slot."""
+        """``layers``: a :class:`StateSpec` per layer record, or ``(kv_heads, dim)`` for a record with keys and values of
+        one size and two tap-mix tails.  ``max_tokens``: the most tokens all live sequences hold at one time; the pool gets
+        that many tokens' worth of pages plus one partly filled page per slot."""
         if page_size <= 0 or max_tokens <= 0 or max_sequences <= 0:
             raise ValueError("page_size, max_tokens and max_sequences must be positive")
         self.device = torch.device(device)
@@ -40,14 +63,21 @@ class PagedState:
         self.max_pages = -(-longest // self.page_size)
         self.n_pages = -(-int(max_tokens) // self.page_size) + self.n_slots
         self.taps = int(taps)
-        # K (normed keys) and V (raw keys) pages per layer: [page][kv head][page_size][dim], float32
-        self.k_pages = [torch.zeros((self.n_pages, g, self.page_size, d), dtype=torch.float32, device=self.device)
-                        for g, d in layers]
-        self.v_pages = [torch.zeros_like(k) for k in self.k_pages]
-        # the last taps - 1 normed inputs of both sublayers of every layer: [slot][taps - 1][width]
+        self.specs = [sp if isinstance(sp, StateSpec) else StateSpec(kv=(sp[0], sp[1], sp[1]), tap_tails=2) for sp in layers]
+        f32 = dict(dtype=torch.float32, device=self.device)
+        # K and V pages per record: [page][kv head][page_size][size], float32 (None for a record without attention)
+        self.k_pages = [torch.zeros((self.n_pages, sp.kv[0], self.page_size, sp.kv[1]), **f32) if sp.kv else None
+                        for sp in self.specs]
+        self.v_pages = [torch.zeros((self.n_pages, sp.kv[0], self.page_size, sp.kv[2]), **f32) if sp.kv else None
+                        for sp in self.specs]
+        # the last taps - 1 normed inputs of the tap-mix sublayers of every record: [slot][taps - 1][width]
         t1 = max(self.taps - 1, 1)
-        self.tails = [(torch.zeros((self.n_slots, t1, width), dtype=torch.float32, device=self.device),
-                       torch.zeros((self.n_slots, t1, width), dtype=torch.float32, device=self.device)) for _ in layers]
+        self.tails = [tuple(torch.zeros((self.n_slots, t1, width), **f32) for _ in range(sp.tap_tails)) for sp in self.specs]
+        # recurrent matrix states [slot][head][value channel][key channel] and short-convolution tails [slot][taps - 1][channels]
+        self.rec_states = [torch.zeros((self.n_slots, sp.recurrent[0], sp.recurrent[1], sp.recurrent[2]), **f32)
+                           if sp.recurrent else None for sp in self.specs]
+        self.conv_tails = [torch.zeros((self.n_slots, max(sp.conv[0] - 1, 1), sp.conv[1]), **f32) if sp.conv else None
+                           for sp in self.specs]
         self._table_host = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32).pin_memory() \
             if self.device.type == "cuda" else torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32)
         self.page_table = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32, device=self.device)
@@ -55,6 +85,10 @@ class PagedState:
         self._free_pages = list(range(self.n_pages - 1, -1, -1))        # pop() takes page 0 first
         self._free_slots = list(range(self.n_slots - 1, -1, -1))
         self.sequences: dict[str, Sequence] = {}
+
+    def record_state(self, i: int) -> "RecordState":
+        """The buffers of layer record ``i`` (what its ``fill`` points the kernels at)."""
+        return RecordState(self.k_pages[i], self.v_pages[i], self.tails[i], self.rec_states[i], self.conv_tails[i])
 
     # ---- bookkeeping -----------------------------------------------------------------------------------------
     @property

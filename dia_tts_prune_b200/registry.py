@@ -46,13 +46,14 @@ def _ensure_builtin() -> None:
             raise FileNotFoundError(f"no Dia checkpoint (*.pth) in {folder}")
         return Dia.from_local(str(folder / "config.json"), str(ckpt), compute_dtype=dtype, device=device)
 
-    def _load_pubopel(folder, dtype="bfloat16", device=None, **kw):
+    def _load_causal_lm(folder, dtype="bfloat16", device=None, **kw):
         from .lm_model import CausalLM
         return CausalLM.from_pretrained(folder, dtype=dtype, device=device, **kw)
 
     register("dia", _load_dia)
     register("DiaModel", _load_dia)
-    register("Pubopel", _load_pubopel)
+    register("Pubopel", _load_causal_lm)
+    register("Kupelix", _load_causal_lm)
 
 
 def load_model(folder: str | Path, dtype: str = "bfloat16", device=None, **kw):

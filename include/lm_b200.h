@@ -4,10 +4,14 @@
  * success or a negative code, nothing throws, a forward call neither allocates nor synchronises.  There is no CPU
  * fallback: every compute entry point launches kernels.
  *
- * A model is a stack of layers  x += norm_b(mixer(tapmix(norm_a(x))));  x += norm_b'(ff(tapmix'(norm_a'(x))))  described
- * by lm_b200_layer records: the mechanisms are selected and parameterised per layer, so another design can combine them
- * differently.  Matrices are bf16 [out][in]; vectors and scalars fp32.  The residual stream, norms, the router,
- * attention scores and the K/V pages are fp32; the operands of the matrix products are fp32 or bf16 (lm_b200_precision).
+ * A model is a stack of layer records.  A record has one of two forms:
+ *   sequential  x += norm_b(mixer(tapmix(norm_a(x))));  x += norm_b'(ff(tapmix'(norm_a'(x))))
+ *   parallel    h = norm_a(x);  x += mixer(h) + ff(h)
+ * and the mechanisms (norm kind, mixer kind, feed-forward kind) are selected and parameterised per record, so a design
+ * combines them as it needs.  A layer that a design runs several times with the same weights is several records that
+ * share weight pointers and differ in their state pointers.  Matrices are bf16 [out][in]; vectors and scalars fp32.
+ * The residual stream, norms, the router, attention scores, the K/V pages, recurrent states and everything that enters
+ * a recurrence are fp32; the operands of the matrix products are fp32 or bf16 (lm_b200_precision).
  *
  * A step is a flat batch of M rows (the new tokens of the scheduled sequences, the rows of one sequence adjacent and in
  * order) described by one int32 device buffer:
@@ -25,21 +29,29 @@
 extern "C" {
 #endif
 
-#define LM_B200_ABI_VERSION 1
+#define LM_B200_ABI_VERSION 2
 
 enum lm_b200_status { LM_B200_OK = 0, LM_B200_EINVAL = -1, LM_B200_ECUDA = -2, LM_B200_ENOMEM = -3, LM_B200_EUNSUPPORTED = -5 };
 
-enum lm_b200_mixer_kind { LM_B200_MIXER_SINK_ATTENTION = 1 };
-enum lm_b200_ff_kind { LM_B200_FF_NONE = 0, LM_B200_FF_ROUTED_EXPERTS = 1 };
+enum lm_b200_mixer_kind {
+    LM_B200_MIXER_SINK_ATTENTION = 1,   /* values = projected keys, whole-projection norms, window, distance bias, sink */
+    LM_B200_MIXER_TALK_ATTENTION = 2,   /* biased q/k/v, per-head norms, rotary positions, scores mixed across heads, sink, gate */
+    LM_B200_MIXER_HGRN2 = 3,            /* gated linear recurrence: the forget gate also sets the write strength */
+    LM_B200_MIXER_CHANNEL_DELTA = 4     /* gated delta rule with a decay per head and key channel, short convolutions */
+};
+enum lm_b200_ff_kind { LM_B200_FF_NONE = 0, LM_B200_FF_ROUTED_EXPERTS = 1, LM_B200_FF_DENSE = 2 };
+enum lm_b200_norm_kind { LM_B200_NORM_DYT = 0, LM_B200_NORM_LAYER = 1 };
+enum lm_b200_layer_form { LM_B200_FORM_SEQUENTIAL = 0, LM_B200_FORM_PARALLEL = 1 };
+enum lm_b200_act_kind { LM_B200_ACT_XIELU = 1 };
 /* FP32: every product is fp32 FMA arithmetic on the stored weights.  BF16: the products of a long step (a prompt portion)
  * run on the tensor cores with bf16 operands and fp32 accumulation; everything else stays fp32. */
 enum lm_b200_precision { LM_B200_PRECISION_FP32 = 0, LM_B200_PRECISION_BF16 = 1 };
 
-/* DynamicTanh norm: y = tanh(alpha x) w + b */
+/* DYT: y = tanh(alpha x) w + b.  LAYER: y = (x - mean) / sqrt(var + eps) * w + b with the model's eps. */
 typedef struct lm_b200_norm {
     const float *w, *b;
     float alpha;
-    int32_t reserved;
+    int32_t kind;                  /* lm_b200_norm_kind */
 } lm_b200_norm;
 
 typedef struct lm_b200_layer {
@@ -59,12 +71,40 @@ typedef struct lm_b200_layer {
     const void *w_gate_up;         /* [experts][2 * expert_ff][width]: gate rows, then up rows */
     const void *w_down;            /* [experts][width][expert_ff] */
     const void *ws_gate_up, *ws_down; /* the shared expert, same form with shared_ff */
-    float *k_pages, *v_pages;      /* [pages][kv_heads][page_size][dim] */
+    float *k_pages, *v_pages;      /* [pages][kv_heads][page_size][dim]; the value pages of a talk attention have [vdim] rows */
     float *tail_mix, *tail_ff;     /* [slots][taps - 1][width]: last normed inputs of each sublayer per sequence */
+
+    /* ---- the parallel form and its mechanisms (all zero / NULL in a sequential record) ---- */
+    int32_t form;                  /* lm_b200_layer_form */
+    int32_t vdim;                  /* value size per head (the sink attention above has vdim = dim and ignores this) */
+    int32_t rot_dims;              /* leading channels of every q / k head that turn with the position (pairs 2i, 2i+1); 0: none */
+    int32_t conv_taps;             /* taps of the short causal convolutions of q, k, v (channel delta) */
+    int32_t rank_a, rank_g;        /* inner sizes of the two-step decay and gate projections (channel delta) */
+    int32_t dense_ff, act;         /* hidden size of the dense feed-forward; lm_b200_act_kind */
+    float act_p, act_q;            /* xIELU: z > 0: act_p z^2 + z / 2;  z <= 0: act_q (e^z - 1 - z) + z / 2 */
+    float unit_eps;                /* inside the root of the unit-vector norm of q and k (channel delta) */
+    int32_t n_in, k_out;           /* rows of w_in (padded to a multiple of 4); columns of w_out */
+    /* every projection that reads h, stacked [n_in][width], in this order and then the feed-forward's up rows:
+     *   TALK_ATTENTION  q (heads*dim) | k (kv_heads*dim) | v (kv_heads*vdim) | gate (heads)
+     *   HGRN2           q (heads*dim) | f (heads*dim) | v (heads*vdim)
+     *   CHANNEL_DELTA   q (kv_heads*dim) | k (kv_heads*dim) | v (heads*vdim) | beta (heads) | a1 (rank_a) | g1 (rank_g) */
+    const void *w_in;
+    const float *in_bias;          /* [n_in] added to the stacked projections where a mechanism has biases; NULL: none */
+    const void *w_out;             /* [width][k_out]: the mixer's output projection beside the feed-forward's down projection */
+    const void *w_pre;             /* [width][2 width]: x <- w_pre [x; embedding output] before this record; NULL: none */
+    const float *rot_freq;         /* [rot_dims / 2] angle per position of every rotary pair */
+    const float *talk;             /* [heads][heads] score_h <- sum_g talk[h][g] score_g before the softmax; NULL: none */
+    const float *head_norm;        /* [vdim] weight of the per-head RMS norm of a recurrent mixer's read-out */
+    const float *lower;            /* [heads*dim] lower bound of the forget gate (HGRN2) */
+    const float *conv_w;           /* [2 kv_heads*dim + heads*vdim][conv_taps]: q, k, v channels; the last tap is the current token's */
+    const float *a_log, *dt_bias;  /* [heads], [heads*dim]: decay = exp(-exp(a_log_h) softplus(a2 a1 h + dt_bias)) */
+    const float *w_a2, *w_g2;      /* [heads*dim][rank_a], [heads*vdim][rank_g] second steps of the decay and gate projections */
+    float *rec_state;              /* [slots][heads][vdim][dim] recurrent state per sequence (column of a value channel contiguous) */
+    float *conv_tail;              /* [slots][conv_taps - 1][2 kv_heads*dim + heads*vdim] last projected inputs per sequence */
 } lm_b200_layer;
 
 typedef struct lm_b200_model {
-    int32_t n_layer, width, vocab, taps;
+    int32_t n_layer, width, vocab, taps;             /* n_layer: layer records in execution order */
     int32_t page_size, max_pages, n_slots, max_rows; /* max_pages: per sequence; max_rows: rows of one forward call */
     float eps;                     /* inside the root of every RMS norm */
     int32_t precision;             /* lm_b200_precision */
@@ -72,7 +112,7 @@ typedef struct lm_b200_model {
     lm_b200_norm final_norm;
     const int32_t *page_table;     /* device, [n_slots][max_pages] */
     int32_t step_graphs;           /* != 0: steps of a few rows (decoding) replay a CUDA graph captured at their first use */
-    int32_t reserved;
+    float logit_scale;             /* multiplies the logits (0 is read as 1) */
 } lm_b200_model;
 
 typedef struct lm_b200_engine lm_b200_engine;
