@@ -216,3 +216,60 @@ def forward(cfg, w, tokens, dtype=torch.float64):
         streams.append(x)
     hN = layer_norm(x, w["final.norm"].to(dtype), w["final.norm.b"].to(dtype), eps)
     return hN @ w["head"].to(dtype).T * float(cfg["logit_scale"]), torch.stack(streams)
+
+
+def greedy(cfg, w, prompt, n_new, dtype=torch.float64):
+    """Greedy continuation by recomputing the whole sequence for every new token; also the logits that chose each token."""
+    toks, rows = list(prompt), []
+    for _ in range(n_new):
+        logits, _ = forward(cfg, w, toks, dtype)
+        rows.append(logits[-1])
+        toks.append(int(torch.argmax(logits[-1])))
+    return toks[len(prompt):], torch.stack(rows)
+
+
+def random_weights(cfg, seed, spread=1.0):
+    """Random bfloat16-representable weights with the checkpoint's names and shapes, for small test models."""
+    g = torch.Generator().manual_seed(seed)
+    D, V = cfg["width"], cfg["vocab"]
+
+    def mat(o, i, s=1.0):
+        return (torch.randn(o, i, generator=g) * (s * spread / math.sqrt(i))).to(torch.bfloat16).to(torch.float32)
+
+    def vec(n, mean=0.0, s=1.0):
+        return (mean + s * torch.randn(n, generator=g)).to(torch.bfloat16).to(torch.float32)
+
+    w = {"embed": vec(V * D).reshape(V, D), "head": mat(V, D), "final.norm": vec(D, 1.0, 0.1), "final.norm.b": vec(D, 0.0, 0.05)}
+    if cfg.get("loop"):
+        w["loop.in"] = mat(D, 2 * D, 1.4)
+    for i, lc in enumerate(cfg["layers"]):
+        L, m = f"l{i}.", lc["mixer"]
+        w[L + "norm1"], w[L + "norm1.b"] = vec(D, 1.0, 0.1), vec(D, 0.0, 0.05)
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        G = m.get("kv_heads") or H
+        if lc["type"] == "attention":
+            w[L + "mix.q"], w[L + "mix.k"], w[L + "mix.v"] = mat(H * d, D, 2.0), mat(G * d, D, 2.0), mat(G * dv, D)
+            w[L + "mix.q.b"], w[L + "mix.k.b"], w[L + "mix.v.b"] = vec(H * d, 0.0, 0.2), vec(G * d, 0.0, 0.2), vec(G * dv, 0.0, 0.2)
+            w[L + "mix.q.norm"], w[L + "mix.k.norm"] = vec(d, 1.0, 0.2), vec(d, 1.0, 0.2)
+            w[L + "mix.talk"] = (torch.eye(H) + 0.4 * torch.randn(H, H, generator=g) / math.sqrt(H)).to(torch.bfloat16).to(torch.float32)
+            w[L + "mix.sink"], w[L + "mix.g"] = vec(H, 0.5, 1.0), mat(H, D, 2.0)
+            w[L + "mix.o"] = mat(D, H * dv)
+        elif lc["type"] == "hgrn2":
+            w[L + "mix.q"], w[L + "mix.f"], w[L + "mix.v"] = mat(H * d, D, 2.0), mat(H * d, D, 2.0), mat(H * dv, D)
+            w[L + "mix.f.b"] = vec(H * d, 1.0, 1.0)
+            w[L + "mix.lower"] = torch.rand(H * d, generator=g).mul(0.9).to(torch.bfloat16).to(torch.float32)
+            w[L + "mix.norm"], w[L + "mix.o"] = vec(dv, 1.0, 0.2), mat(D, H * dv)
+        else:
+            taps, ra, rg = m["conv"], lc.get("_rank_a", 6), lc.get("_rank_g", 5)
+            w[L + "mix.q"], w[L + "mix.k"], w[L + "mix.v"] = mat(G * d, D, 2.0), mat(G * d, D, 2.0), mat(H * dv, D, 2.0)
+            for n, c in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                w[L + f"mix.{n}.conv"] = vec(c * taps, 0.0, 0.6).reshape(c, taps)
+            w[L + "mix.b"] = mat(H, D, 2.0)
+            w[L + "mix.A_log"] = torch.log(0.3 + 3.0 * torch.rand(H, generator=g)).to(torch.bfloat16).to(torch.float32)
+            w[L + "mix.a1"], w[L + "mix.a2"], w[L + "mix.dt_bias"] = mat(ra, D, 2.0), mat(H * d, ra, 2.0), vec(H * d, -1.0, 1.0)
+            w[L + "mix.g1"], w[L + "mix.g2"] = mat(rg, D, 2.0), mat(H * dv, rg, 2.0)
+            w[L + "mix.norm"], w[L + "mix.o"] = vec(dv, 1.0, 0.2), mat(D, H * dv)
+        if lc.get("mlp"):
+            F = lc["mlp"]["ff"]
+            w[L + "mlp.up"], w[L + "mlp.down"], w[L + "mlp.act"] = mat(F, D, 2.0), mat(D, F), vec(2, 0.3, 0.7)
+    return w
