@@ -21,7 +21,9 @@ SURVEY.md 8(e)); `value` is the sum over ranks divided by the slowest rank's tim
 
 `--lm` leaves that workload aside and measures the decoder-only language-model path (Pubopel, random weights) at layer
 sizes of a real model: prefill and decode throughput through `CausalLM`, and its GEMM / attention kernels beside Dia's
-at equal size (one JSON line, metric `lm_layer_throughput`).
+at equal size (one JSON line, metric `lm_layer_throughput`).  `--lm --lm-design kupelix` measures the Kupelix design
+instead: its prefill and decode throughput beside Pubopel's at equal width, heads and vocabulary, its attention kernel
+beside Pubopel's on the same causal workload, and its recurrence kernels against the bytes and state updates they must move.
 """
 
 from __future__ import annotations
@@ -641,6 +643,182 @@ def run_lm(args) -> None:
                       "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
 
 
+# ---- --lm --lm-design kupelix: the Kupelix design beside Pubopel at equal width, and its kernels beside Pubopel's ---------
+KUPELIX_SIZES = {
+    # the widths, head shapes and vocabularies of LM_SIZES; a dense feed-forward as wide as Pubopel's active hidden units
+    "w2048": dict(width=2048, kinds=["attention", "hgrn2", "channel_delta", "attention"], heads=16, kv_heads=4, dim=128, vdim=128,
+                  ff=8192, vocab=32768),
+    "w1024": dict(width=1024, kinds=["attention", "hgrn2", "channel_delta", "attention"], heads=8, kv_heads=2, dim=128, vdim=128,
+                  ff=2048, vocab=16384),
+}
+
+
+def _lm_prefill_decode(model, toks, T, ctx, W, K, flush) -> dict:
+    """Prefill of one T-token prompt and teacher-forced decoding of 1 and 8 sequences at `ctx` tokens, device-timed."""
+    def prefill():
+        model.run_step([{"id": "p", "tokens": toks, "want": [T - 1]}], ["p"])
+    ms = _event_ms(prefill, W, K, flush)
+    res = {"prefill": {"tokens": T, "ms": ms, "tokens_per_s": T / ms * 1e3}}
+    for B in (1, 8):
+        for b in range(B):
+            model.run_step([{"id": f"d{b}", "tokens": toks[:ctx], "want": []}])
+        n_dec = 32
+        def decode():
+            for t in range(n_dec):
+                model.run_step([{"id": f"d{b}", "tokens": [toks[(ctx + t) % T]], "want": [0]} for b in range(B)])
+        ms = _event_ms(decode, 1, K) / n_dec
+        for b in range(B):
+            model.state.close(f"d{b}")
+        res[f"decode_b{B}"] = {"context": ctx, "ms_per_step": ms, "tokens_per_s": B / ms * 1e3}
+    return res
+
+
+def run_lm_kupelix(args) -> None:
+    import torch
+    from dia_tts_prune_b200 import synthetic as SY
+    from dia_tts_prune_b200.lm_config import KupelixConfig, PubopelConfig
+    from dia_tts_prune_b200.lm_engine import launch_count
+    from dia_tts_prune_b200.lm_model import CausalLM
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        hbm, tf, src = float(pk["hbm_gbs"]), float(pk["bf16_tflops"]), "measured"
+    except Exception:
+        hbm, tf, src = 6650.0, 1590.0, "fallback"
+    flush = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)             # > the 126 MB L2
+    W, K = max(args.warmup, 3), max(args.steps, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    out = {}
+    T, ctx, R = args.lm_prompt, args.lm_context, args.lm_rows
+    for name in (args.lm_sizes.split(",") if args.lm_sizes else KUPELIX_SIZES):
+        sz, psz = KUPELIX_SIZES[name], LM_SIZES[name]
+        D, H, G, d, dv, F, V = sz["width"], sz["heads"], sz["kv_heads"], sz["dim"], sz["vdim"], sz["ff"], sz["vocab"]
+        toks = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(7)).tolist()
+        cap = max(T, 8 * (ctx + 32 * (K + 2))) + 64
+        res = {"config": sz}
+        # -- the whole models: Kupelix, then Pubopel of the same width, heads and vocabulary
+        cfg = SY.kupelix_config(**sz)
+        model = CausalLM(KupelixConfig.model_validate(cfg), SY.kupelix_weights(cfg, WEIGHT_SEED, dev), dtype="bfloat16", device=dev,
+                         max_tokens=cap, max_sequences=8, page_size=64, max_rows=R)
+        res["kupelix"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        n_att = sz["kinds"].count("attention")
+        L = len(sz["kinds"])
+        per_layer = {"attention": H * d + G * d + G * dv + H, "hgrn2": 2 * H * d + H * dv,
+                     "channel_delta": 2 * H * d + H * dv + H + 128}
+        w_bytes = 2.0 * (sum(D * (per_layer[k] + F) + D * (H * dv + F) for k in sz["kinds"]) + D * V)
+        state_bytes = 8.0 * H * d * dv * (L - n_att) + 4.0 * ctx * G * (d + dv) * n_att    # states read + written, keys + values read
+        flops = sum(2.0 * T * D * (per_layer[k] + F) + 2.0 * T * D * (H * dv + F) for k in sz["kinds"]) + \
+            n_att * 2.0 * H * (d + dv) * T * (T + 1) / 2 + (L - n_att) * 6.0 * T * H * d * dv + 2.0 * D * V
+        res["kupelix"]["prefill"].update(model_tflops=flops / res["kupelix"]["prefill"]["ms"] / 1e9,
+                                         frac_of_bf16_peak=flops / res["kupelix"]["prefill"]["ms"] / 1e9 / tf)
+        b1 = res["kupelix"]["decode_b1"]
+        b1.update(algorithmic_bytes=w_bytes + state_bytes, gb_per_s=(w_bytes + state_bytes) / b1["ms_per_step"] / 1e6,
+                  frac_of_hbm_peak=(w_bytes + state_bytes) / b1["ms_per_step"] / 1e6 / hbm)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+        pcfg = SY.pubopel_config(**psz)
+        model = CausalLM(PubopelConfig.model_validate(pcfg), SY.pubopel_weights(pcfg, WEIGHT_SEED, dev), dtype="bfloat16", device=dev,
+                         max_tokens=cap, max_sequences=8, page_size=64, max_rows=R)
+        res["pubopel"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+
+        # -- kernels alone: one-layer models, the mixer kernels on given projections (no products around them)
+        kern = {}
+
+        def one_layer(kind):
+            c1 = SY.kupelix_config(**{**sz, "kinds": [kind], "vocab": 256, "ff": 8})
+            return CausalLM(KupelixConfig.model_validate(c1), SY.kupelix_weights(c1, 3, dev), dtype="float32", device=dev,
+                            max_tokens=8 * T + 64, max_sequences=8, page_size=64, max_rows=R)
+
+        def timed_mixer(m1, n_seq, rows_each, start):
+            """rows_each new rows for each of n_seq sequences that already hold `start` tokens (state appended each call)."""
+            n_in = m1.layers[0].layer.n_in
+            proj = torch.randn(n_seq * min(rows_each, R), n_in, device=dev) * 0.5
+            seqs = [m1.state.open(f"s{i}") for i in range(n_seq)]
+            for sq in seqs:
+                m1.state.reserve(sq, start + rows_each)
+            def run():
+                for r0 in range(0, rows_each, R):
+                    n = min(R, rows_each - r0)
+                    m1.engine.op_mixer_kernels(0, proj[:n_seq * n], [(sq, n, start + r0) for sq in seqs])
+            ms = _event_ms(run, 2, K, flush)
+            for i in range(n_seq):
+                m1.state.close(f"s{i}")
+            return ms
+
+        m1 = one_layer("attention")
+        a_flops = 2.0 * H * (d + dv) * T * (T + 1) / 2
+        ms_k = timed_mixer(m1, 1, T, 0)
+        kern["attention_causal"] = {"T": T, "heads": H, "kv_heads": G, "dim": d, "vdim": dv, "kupelix_ms": ms_k,
+                                    "kupelix_tflops_fp32": a_flops / ms_k / 1e9}
+        ms_k = timed_mixer(m1, 8, 1, ctx)                        # eight decoding rows, each over ctx keys (written by the call before)
+        kv_bytes = 8.0 * ctx * G * (d + dv) * 4
+        kern["attention_decode_b8"] = {"context": ctx, "kupelix_ms": ms_k, "kupelix_gb_per_s": kv_bytes / ms_k / 1e6,
+                                       "kupelix_frac_of_hbm_peak": kv_bytes / ms_k / 1e6 / hbm}
+        m1.engine.close()
+        full_cfg = SY.pubopel_config(**{**psz, "layers": 1, "window": None, "vocab": 256, "experts": 1, "top": 1, "expert_ff": 8,
+                                        "shared_ff": None})
+        full = CausalLM(PubopelConfig.model_validate(full_cfg), SY.pubopel_weights(full_cfg, 3, dev), dtype="float32", device=dev,
+                        max_tokens=8 * T + 64, max_sequences=8, page_size=64, max_rows=R)
+        qk = torch.randn(T, (H + G) * d, device=dev)
+
+        def pub_attn(n_seq, rows_each, start):
+            seqs = [full.state.open(f"s{i}") for i in range(n_seq)]
+            for sq in seqs:
+                full.state.reserve(sq, start + rows_each)
+            def run():
+                for r0 in range(0, rows_each, R):
+                    n = min(R, rows_each - r0)
+                    full.engine.op_attention(0, qk[:n_seq * n], [(sq, n, start + r0) for sq in seqs])
+            ms = _event_ms(run, 2, K, flush)
+            for i in range(n_seq):
+                full.state.close(f"s{i}")
+            return ms
+        ms_p = pub_attn(1, T, 0)
+        kern["attention_causal"].update(pubopel_ms=ms_p, pubopel_tflops_fp32=4.0 * d * H * T * (T + 1) / 2 / ms_p / 1e9)
+        ms_p = pub_attn(8, 1, ctx)
+        pk_bytes = 8.0 * ctx * G * 2 * d * 4
+        kern["attention_decode_b8"].update(pubopel_ms=ms_p, pubopel_gb_per_s=pk_bytes / ms_p / 1e6,
+                                           pubopel_frac_of_hbm_peak=pk_bytes / ms_p / 1e6 / hbm)
+        full.engine.close()
+        del full, m1
+        torch.cuda.empty_cache()
+        for kind in ("hgrn2", "channel_delta"):
+            m1 = one_layer(kind)
+            n_in = m1.layers[0].layer.n_in
+            ent = {}
+            for label, (n_seq, rows_each, start) in {"prefill_1x%d" % T: (1, T, 0), "prefill_8x512": (8, 512, 0),
+                                                     "decode_b8": (8, 1, 64)}.items():
+                ms_k = timed_mixer(m1, n_seq, rows_each, start)
+                rows = n_seq * rows_each
+                byt = rows * 4.0 * (n_in + H * dv) + n_seq * 8.0 * H * d * dv          # projections in, read-out, states in and out
+                ent[label] = {"ms": ms_k, "rows_per_s": rows / ms_k * 1e3, "gb_per_s": byt / ms_k / 1e6,
+                              "frac_of_hbm_peak": byt / ms_k / 1e6 / hbm,
+                              "state_tflops_fp32": (6.0 if kind == "hgrn2" else 10.0) * rows * H * d * dv / ms_k / 1e9}
+            kern[kind + "_recurrence"] = ent
+            m1.engine.close()
+            del m1
+            torch.cuda.empty_cache()
+        res["kernels"] = kern
+        out[name] = res
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "lm_layer_throughput", "design": "kupelix", "impl": "ours", "n_gpus": 1, "steps": K, "warmup": W,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids)",
+                      "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+                      "timing": "CUDA events, median; a 160 MB buffer is rewritten between timed iterations (L2 flush)",
+                      "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -663,12 +841,16 @@ def main():
     ap.add_argument("--lm", action="store_true",
                     help="instead of the headline workload: prefill / decode throughput of the decoder-only language-model path "
                          "(Pubopel, random weights) at layer sizes of a real model, beside Dia's kernels at equal size")
+    ap.add_argument("--lm-design", default="pubopel", choices=["pubopel", "kupelix"],
+                    help="--lm: the design that is measured (kupelix: beside Pubopel at equal width, and its kernels beside Pubopel's)")
     ap.add_argument("--lm-sizes", default="", help="--lm: comma-separated subset of " + ",".join(LM_SIZES))
     ap.add_argument("--lm-prompt", type=int, default=4096, help="--lm: prompt tokens of the prefill measurement")
     ap.add_argument("--lm-rows", type=int, default=4096, help="--lm: most rows of one engine step (longer prompts run in portions)")
     ap.add_argument("--lm-context", type=int, default=1024, help="--lm: tokens each sequence holds before the decode measurement")
     args = ap.parse_args()
-    if args.lm:
+    if args.lm and args.lm_design == "kupelix":
+        run_lm_kupelix(args)
+    elif args.lm:
         run_lm(args)
         return
     if args.impl == "reference":

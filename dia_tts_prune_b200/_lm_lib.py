@@ -60,6 +60,7 @@ _SIGNATURES = {
     "lm_b200_op_norm_tapmix": (_ci, [_vp, _ci, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
     "lm_b200_op_mixer": (_ci, [_vp, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
     "lm_b200_op_attention": (_ci, [_vp, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
+    "lm_b200_op_mixer_kernels": (_ci, [_vp, _ci, _vp, _vp, _ci, _ci, _vp, _vp]),
     "lm_b200_op_ff": (_ci, [_vp, _ci, _vp, _ci, _vp, _vp]),
     "lm_b200_op_linear": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "lm_b200_op_linear_tc": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),

@@ -355,6 +355,47 @@ int product(lm_b200_engine* e, const float* A, const void* Ab, int lda, const vo
     return LM_B200_OK;
 }
 
+// the mixer's own kernels on the stacked projections proj [M][c.n] (modified in place): the mixer's output lands in the
+// first columns of e->outcat [M][k_out] (and its bf16 copy ob, if given)
+int mixer_kernels(lm_b200_engine* e, const lm_b200_layer& l, const InCols& c, float* proj, const StepView& v, int M, int n_seq,
+                  void* ob, cudaStream_t st) {
+    const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
+    const int ko = l.k_out;
+    switch (l.mixer) {
+        case LM_B200_MIXER_TALK_ATTENTION: {
+            const lm::TalkShape a = talk_shape(l);
+            LCK(lm::launch_talk_prep(proj, c.n, l.in_bias, c.q, c.k, c.v, c.gate, a, l.q_norm, l.k_norm, e->m.eps, l.k_pages,
+                                     l.v_pages, pm, v.rm, M, st));
+            LCK(lm::launch_talk_attention(proj, c.n, c.q, c.gate, l.k_pages, l.v_pages, pm, a, v.rm, e->outcat, ko, ob,
+                                          e->split_ws, e->split_arrived, M, st));
+            break;
+        }
+        case LM_B200_MIXER_HGRN2: {
+            const lm::ScanInputs si{c.q, 0, c.f, c.v, 0, l.in_bias, l.lower};
+            LCK(lm::launch_column_scan(proj, c.n, si, false, l.heads, l.heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
+                                       e->outcat, ko, st));
+            LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, nullptr, 0, l.heads, l.vdim, e->m.eps, M, st));
+            break;
+        }
+        case LM_B200_MIXER_CHANNEL_DELTA: {
+            const lm::DeltaShape d{l.heads, l.kv_heads, l.dim, l.vdim, l.conv_taps, l.rank_a, l.rank_g, l.unit_eps, l.conv_w,
+                                   l.a_log, l.dt_bias, l.w_a2, l.w_g2};
+            const int ldr = rec_cols(l), C = 2 * l.kv_heads * l.dim + l.heads * l.vdim;
+            LCK(lm::launch_delta_prep(proj, c.n, c.beta, c.a1, c.g1, d, l.conv_tail, v.rm, e->rec, ldr, M, st));
+            LCK(lm::launch_conv_tail(proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
+            const int k0 = l.kv_heads * l.dim, v0 = 2 * k0, d0 = v0 + l.heads * l.vdim, g0 = d0 + l.heads * l.dim,
+                      b0 = g0 + l.heads * l.vdim;
+            const lm::ScanInputs si{0, k0, d0, v0, b0, nullptr, nullptr};
+            LCK(lm::launch_column_scan(e->rec, ldr, si, true, l.heads, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
+                                       e->outcat, ko, st));
+            LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, e->rec + g0, ldr, l.heads, l.vdim, e->m.eps, M, st));
+            break;
+        }
+        default: return LM_B200_EUNSUPPORTED;
+    }
+    return LM_B200_OK;
+}
+
 // One record of the parallel form.  only == 0: x += mixer(h) + ff(h) with h = norm(x) (after the input mix, if the record
 // has one).  only == 1 / 2: y = mixer(h_in) / ff(h_in) alone for a given h_in (operator boundaries).
 int parallel_layer(lm_b200_engine* e, const lm_b200_layer& l, const StepView& v, int M, int n_seq, int only, const float* h_in,
@@ -362,7 +403,6 @@ int parallel_layer(lm_b200_engine* e, const lm_b200_layer& l, const StepView& v,
     const int D = e->m.width;
     const bool bf = e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin;
     const InCols c = in_cols(l);
-    const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
     const float* h = h_in;
     const void* hb = nullptr;
     if (only == 0) {
@@ -388,38 +428,8 @@ int parallel_layer(lm_b200_engine* e, const lm_b200_layer& l, const StepView& v,
         if (ob && cudaMemsetAsync(ob, 0, (size_t)M * ko * 2, st) != cudaSuccess) return cuda_fail(cudaGetLastError());
     }
     if (only != 2) {
-        switch (l.mixer) {
-            case LM_B200_MIXER_TALK_ATTENTION: {
-                const lm::TalkShape a = talk_shape(l);
-                LCK(lm::launch_talk_prep(e->proj, c.n, l.in_bias, c.q, c.k, c.v, c.gate, a, l.q_norm, l.k_norm, e->m.eps, l.k_pages,
-                                         l.v_pages, pm, v.rm, M, st));
-                LCK(lm::launch_talk_attention(e->proj, c.n, c.q, c.gate, l.k_pages, l.v_pages, pm, a, v.rm, e->outcat, ko, ob,
-                                              e->split_ws, e->split_arrived, M, st));
-                break;
-            }
-            case LM_B200_MIXER_HGRN2: {
-                const lm::ScanInputs si{c.q, 0, c.f, c.v, 0, l.in_bias, l.lower};
-                LCK(lm::launch_column_scan(e->proj, c.n, si, false, l.heads, l.heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
-                                           e->outcat, ko, st));
-                LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, nullptr, 0, l.heads, l.vdim, e->m.eps, M, st));
-                break;
-            }
-            case LM_B200_MIXER_CHANNEL_DELTA: {
-                const lm::DeltaShape d{l.heads, l.kv_heads, l.dim, l.vdim, l.conv_taps, l.rank_a, l.rank_g, l.unit_eps, l.conv_w,
-                                       l.a_log, l.dt_bias, l.w_a2, l.w_g2};
-                const int ldr = rec_cols(l), C = 2 * l.kv_heads * l.dim + l.heads * l.vdim;
-                LCK(lm::launch_delta_prep(e->proj, c.n, c.beta, c.a1, c.g1, d, l.conv_tail, v.rm, e->rec, ldr, M, st));
-                LCK(lm::launch_conv_tail(e->proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
-                const int k0 = l.kv_heads * l.dim, v0 = 2 * k0, d0 = v0 + l.heads * l.vdim, g0 = d0 + l.heads * l.dim,
-                          b0 = g0 + l.heads * l.vdim;
-                const lm::ScanInputs si{0, k0, d0, v0, b0, nullptr, nullptr};
-                LCK(lm::launch_column_scan(e->rec, ldr, si, true, l.heads, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
-                                           e->outcat, ko, st));
-                LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, e->rec + g0, ldr, l.heads, l.vdim, e->m.eps, M, st));
-                break;
-            }
-            default: return LM_B200_EUNSUPPORTED;
-        }
+        rc = mixer_kernels(e, l, c, e->proj, v, M, n_seq, ob, st);
+        if (rc) return rc;
     }
     if (only != 1 && l.ff == LM_B200_FF_DENSE)
         LCK(lm::launch_xielu_rows(e->proj, c.n, c.up, l.act_p, l.act_q, e->outcat, ko, c.mix_out, ob, M, l.dense_ff, st));
@@ -701,6 +711,22 @@ int lm_b200_op_attention(lm_b200_engine* e, int layer, float* qk, const int32_t*
                                  S(stream)));
     const lm::AttnShape a{l.heads, l.kv_heads, l.dim, l.window, l.keep_first, l.scale, l.softcap, l.temp, l.slopes, l.sink};
     LCK(lm::launch_sink_attention(qk, nq + nk, l.k_pages, l.v_pages, pm, a, v.rm, out, nullptr, e->split_ws, e->split_arrived, M, S(stream)));
+    return LM_B200_OK;
+}
+
+int lm_b200_op_mixer_kernels(lm_b200_engine* e, int layer, float* proj, const int32_t* step, int M, int n_seq, float* out,
+                             void* stream) {
+    if (!e || layer < 0 || layer >= e->m.n_layer || !proj || !step || !out || M <= 0 || M > e->m.max_rows || n_seq <= 0)
+        return LM_B200_EINVAL;
+    const lm_b200_layer& l = e->layers[layer];
+    if (l.form != LM_B200_FORM_PARALLEL) return LM_B200_EUNSUPPORTED;
+    Guard g(e->device);
+    if (!g.ok) return LM_B200_ECUDA;
+    const int rc = mixer_kernels(e, l, in_cols(l), proj, view(step, M, n_seq), M, n_seq, nullptr, S(stream));
+    if (rc) return rc;
+    const size_t w = (size_t)l.heads * l.vdim * 4;
+    if (cudaMemcpy2DAsync(out, w, e->outcat, (size_t)l.k_out * 4, w, M, cudaMemcpyDeviceToDevice, S(stream)) != cudaSuccess)
+        return cuda_fail(cudaGetLastError());
     return LM_B200_OK;
 }
 

@@ -192,6 +192,18 @@ class LMEngine:
                                                     _stream(self.device)), "op_attention")
         return out
 
+    def op_mixer_kernels(self, layer: int, proj: torch.Tensor, parts) -> torch.Tensor:
+        """The mixer kernels of a parallel-form record alone on stacked projections ``proj [M, n_in]`` (its attention or
+        recurrence without the products around it); the state of the sequences in ``parts`` is appended to."""
+        buf, M, S, _ = self._pack([(s, [0] * n, p0, []) for s, n, p0 in parts])
+        self.state.sync_table()
+        m = self.layers[layer].mixer
+        proj = proj.to(device=self.device, dtype=torch.float32).contiguous().clone()
+        out = torch.empty((M, m.heads * m.vdim), dtype=torch.float32, device=self.device)
+        _lm_lib.check(self.lib.lm_b200_op_mixer_kernels(self._h, layer, proj.data_ptr(), buf.data_ptr(), M, S, out.data_ptr(),
+                                                        _stream(self.device)), "op_mixer_kernels")
+        return out
+
     def op_ff(self, layer: int, h: torch.Tensor) -> torch.Tensor:
         h = h.to(device=self.device, dtype=torch.float32).contiguous()
         y = torch.empty_like(h)

@@ -284,19 +284,19 @@ class ParallelLayer:
 
     def __init__(self, norm: LayerNorm, mixer, ff: DenseXielu | None, device):
         self.norm, self.mixer, self.ff = norm, mixer, ff
-        rows = list(mixer.in_rows) + ([ff.w_up] if ff is not None else [])
+        rows = [_bf16(r, device) for r in list(mixer.in_rows) + ([ff.w_up] if ff is not None else [])]
         n = sum(int(r.shape[0]) for r in rows)
         self.n_in = (n + 3) & ~3
         width = int(rows[0].shape[1])
         if self.n_in > n:
-            rows.append(torch.zeros((self.n_in - n, width), dtype=rows[0].dtype))
-        self.w_in = _bf16(torch.cat([r.to(torch.float32) for r in rows], dim=0), device)
+            rows.append(torch.zeros((self.n_in - n, width), dtype=torch.bfloat16, device=device))
+        self.w_in = torch.cat(rows, dim=0).contiguous()
         self.in_bias = None
         if mixer.has_bias:
-            b = torch.cat([x.to(torch.float32).reshape(-1) for x in mixer.in_bias])
-            self.in_bias = _f32(torch.cat([b, torch.zeros(self.n_in - b.numel())]), device)
-        outs = [mixer.w_o] + ([ff.w_down] if ff is not None else [])
-        self.w_out = _bf16(torch.cat([o.to(torch.float32) for o in outs], dim=1), device)
+            b = torch.cat([_f32(x, device).reshape(-1) for x in mixer.in_bias])
+            self.in_bias = torch.cat([b, torch.zeros(self.n_in - b.numel(), dtype=torch.float32, device=device)]).contiguous()
+        outs = [_bf16(o, device) for o in [mixer.w_o] + ([ff.w_down] if ff is not None else [])]
+        self.w_out = torch.cat(outs, dim=1).contiguous()
         self.k_out = int(self.w_out.shape[1])
 
     def state_spec(self) -> StateSpec:

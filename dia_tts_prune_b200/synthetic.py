@@ -145,3 +145,71 @@ def pubopel_weights(cfg: dict, seed: int = 1234, device="cpu") -> dict:
                 sf = f["shared"]["ff"]
                 w[p + "mlp.shared.gate"], w[p + "mlp.shared.up"], w[p + "mlp.shared.down"] = mat(sf, D), mat(sf, D), mat(D, sf)
     return w
+
+
+def kupelix_config(width: int, kinds: list[str], heads: int, kv_heads: int, dim: int, vdim: int, ff: int, vocab: int, taps: int = 4,
+                   loop: dict | None = None) -> dict:
+    """A Kupelix ``config.json`` as a dictionary: one layer per entry of ``kinds`` (``attention`` / ``hgrn2`` /
+    ``channel_delta``), all with the given head sizes and a dense feed-forward of ``ff`` hidden units."""
+    layers = []
+    for kind in kinds:
+        m = {"heads": heads, "dim": dim, "vdim": vdim}
+        if kind == "attention":
+            m.update(kv_heads=kv_heads, scale=dim ** -0.5,
+                     rot={"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+        elif kind == "channel_delta":
+            m.update(kv_heads=heads, conv=taps)
+        layers.append({"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+    cfg = {"architecture": "Kupelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": layers}
+    if loop:
+        cfg["loop"] = dict(loop)
+    return cfg
+
+
+def kupelix_weights(cfg: dict, seed: int = 1234, device="cpu", rank: int = 64) -> dict:
+    """Random bfloat16 tensors under the checkpoint's names: matrices ~ N(0, 1 / fan_in), norms near the identity, gates
+    and decays in their working range."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, V = cfg["width"], cfg["vocab"]
+
+    def mat(n, k, s=1.0):
+        return (torch.randn((n, k), generator=g, device=device) * (s * k ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, mean, spread):
+        return (mean + spread * torch.randn((n,), generator=g, device=device)).to(torch.bfloat16)
+
+    w = {"embed": torch.randn((V, D), generator=g, device=device).to(torch.bfloat16), "head": mat(V, D),
+         "final.norm": vec(D, 1.0, 0.05), "final.norm.b": vec(D, 0.0, 0.02)}
+    if cfg.get("loop"):
+        w["loop.in"] = mat(D, 2 * D, 1.4)
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lc["mixer"]
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        G = m.get("kv_heads") or H
+        w[p + "norm1"], w[p + "norm1.b"] = vec(D, 1.0, 0.05), vec(D, 0.0, 0.02)
+        if lc["type"] == "attention":
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"], w[p + "mix.g"] = mat(H * d, D), mat(G * d, D), mat(G * dv, D), mat(H, D)
+            w[p + "mix.q.b"], w[p + "mix.k.b"], w[p + "mix.v.b"] = vec(H * d, 0.0, 0.1), vec(G * d, 0.0, 0.1), vec(G * dv, 0.0, 0.1)
+            w[p + "mix.q.norm"], w[p + "mix.k.norm"] = vec(d, 1.0, 0.05), vec(d, 1.0, 0.05)
+            w[p + "mix.talk"] = (torch.eye(H, device=device) + 0.3 * H ** -0.5 * torch.randn((H, H), generator=g, device=device)).to(torch.bfloat16)
+            w[p + "mix.sink"] = vec(H, 0.0, 0.5)
+        elif lc["type"] == "hgrn2":
+            w[p + "mix.q"], w[p + "mix.f"], w[p + "mix.v"] = mat(H * d, D), mat(H * d, D), mat(H * dv, D)
+            w[p + "mix.f.b"] = vec(H * d, 1.0, 0.5)
+            w[p + "mix.lower"] = (0.9 * torch.rand((H * d,), generator=g, device=device)).to(torch.bfloat16)
+            w[p + "mix.norm"] = vec(dv, 1.0, 0.05)
+        else:
+            taps = m["conv"]
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"], w[p + "mix.b"] = mat(G * d, D), mat(G * d, D), mat(H * dv, D), mat(H, D)
+            for n, c in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                w[p + f"mix.{n}.conv"] = (0.5 * torch.randn((c, taps), generator=g, device=device)).to(torch.bfloat16)
+            w[p + "mix.A_log"] = torch.log(0.3 + 3.0 * torch.rand((H,), generator=g, device=device)).to(torch.bfloat16)
+            w[p + "mix.a1"], w[p + "mix.a2"], w[p + "mix.dt_bias"] = mat(rank, D), mat(H * d, rank), vec(H * d, -1.0, 0.5)
+            w[p + "mix.g1"], w[p + "mix.g2"] = mat(rank, D), mat(H * dv, rank)
+            w[p + "mix.norm"] = vec(dv, 1.0, 0.05)
+        w[p + "mix.o"] = mat(D, H * dv)
+        if lc.get("mlp"):
+            F = lc["mlp"]["ff"]
+            w[p + "mlp.up"], w[p + "mlp.down"], w[p + "mlp.act"] = mat(F, D), mat(D, F), vec(2, 0.3, 0.3)
+    return w

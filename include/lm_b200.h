@@ -144,6 +144,10 @@ int lm_b200_op_mixer(lm_b200_engine *e, int layer, const float *h, const int32_t
  * norms (q in place), the page append and the attention; out [M][heads * dim] */
 int lm_b200_op_attention(lm_b200_engine *e, int layer, float *qk, const int32_t *step, int M, int n_seq, float *out,
                          void *stream);
+/* a parallel record's mixer kernels alone on given stacked projections proj [M][n_in] (modified in place; state is
+ * appended as in a step): out [M][heads * vdim], before the output projection */
+int lm_b200_op_mixer_kernels(lm_b200_engine *e, int layer, float *proj, const int32_t *step, int M, int n_seq, float *out,
+                             void *stream);
 /* y = ff(h): router, expert groups, shared expert; the sum over a row's experts */
 int lm_b200_op_ff(lm_b200_engine *e, int layer, const float *h, int M, float *y, void *stream);
 /* Y[M][N] = A[M][K] . W[N][K]^T */
