@@ -848,10 +848,8 @@ def main():
     ap.add_argument("--lm-rows", type=int, default=4096, help="--lm: most rows of one engine step (longer prompts run in portions)")
     ap.add_argument("--lm-context", type=int, default=1024, help="--lm: tokens each sequence holds before the decode measurement")
     args = ap.parse_args()
-    if args.lm and args.lm_design == "kupelix":
-        run_lm_kupelix(args)
-    elif args.lm:
-        run_lm(args)
+    if args.lm:
+        (run_lm_kupelix if args.lm_design == "kupelix" else run_lm)(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -23,7 +23,7 @@
 //   [x = [x | x0] W_pre^T]                      pair_rows, linear            (x0: the embedding output; in front of a repeated block)
 //   h = layernorm(x)                            layernorm_rows
 //   proj = h W_in^T                             linear: every projection of the mixer and the feed-forward's up rows
-//   mixer on proj -> out[:, :mixer columns]     talk_prep + talk_attention | column_scan + head_norm_gate |
+//   mixer on proj -> out[:, :mixer columns]     talk_prep + talk_attention | gate_prep + column_scan + head_norm_gate |
 //                                               delta_prep + conv_tail + column_scan + head_norm_gate
 //   out[:, mixer columns:] = act(proj up rows)  xielu_rows
 //   x += out W_out^T                            linear with the residual add (W_out = [W_o | W_down])
@@ -371,7 +371,8 @@ int mixer_kernels(lm_b200_engine* e, const lm_b200_layer& l, const InCols& c, fl
             break;
         }
         case LM_B200_MIXER_HGRN2: {
-            const lm::ScanInputs si{c.q, 0, c.f, c.v, 0, l.in_bias, l.lower};
+            LCK(lm::launch_gate_prep(proj, c.n, c.q, c.f, c.v, l.in_bias, l.lower, l.heads * l.dim, l.heads * l.vdim, M, st));
+            const lm::ScanInputs si{c.q, 0, c.f, c.v, 0};
             LCK(lm::launch_column_scan(proj, c.n, si, false, l.heads, l.heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
                                        e->outcat, ko, st));
             LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, nullptr, 0, l.heads, l.vdim, e->m.eps, M, st));
@@ -385,7 +386,7 @@ int mixer_kernels(lm_b200_engine* e, const lm_b200_layer& l, const InCols& c, fl
             LCK(lm::launch_conv_tail(proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
             const int k0 = l.kv_heads * l.dim, v0 = 2 * k0, d0 = v0 + l.heads * l.vdim, g0 = d0 + l.heads * l.dim,
                       b0 = g0 + l.heads * l.vdim;
-            const lm::ScanInputs si{0, k0, d0, v0, b0, nullptr, nullptr};
+            const lm::ScanInputs si{0, k0, d0, v0, b0};
             LCK(lm::launch_column_scan(e->rec, ldr, si, true, l.heads, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
                                        e->outcat, ko, st));
             LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, e->rec + g0, ldr, l.heads, l.vdim, e->m.eps, M, st));

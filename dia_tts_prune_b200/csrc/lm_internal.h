@@ -82,8 +82,8 @@ struct DeltaShape {
     float unit_eps;
     const float* conv_w; const float* a_log; const float* dt_bias; const float* w_a2; const float* w_g2;
 };
-// columns of the recurrence's inputs in their row; in_bias / lower transform the gate-tied form's inputs (may be null)
-struct ScanInputs { int q_off, k_off, a_off, v_off, beta_off; const float* in_bias; const float* lower; };
+// columns of the recurrence's inputs in their row
+struct ScanInputs { int q_off, k_off, a_off, v_off, beta_off; };
 
 cudaError_t launch_layernorm_rows(const float* x, const int* rows, const float* w, const float* b, float eps, float out_scale,
                                   float* out, void* out_bf16, int M, int D, cudaStream_t st);
@@ -102,6 +102,8 @@ cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, int a1_of
                               const float* tail, const RowMeta& rm, float* rec, int ldr, int M, cudaStream_t st);
 cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* tail, const SeqMeta& sm, int n_seq,
                              cudaStream_t st);
+cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_off, const float* bias, const float* lower, int n_qf,
+                             int n_v, int M, cudaStream_t st);
 cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
                                float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
                                cudaStream_t st);

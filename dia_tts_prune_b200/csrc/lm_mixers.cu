@@ -18,6 +18,7 @@
 //                             tail), unit-vector q and k per head, beta, the per-channel decay and the output gate from
 //                             their two-step projections
 //   conv_tail_kernel          keeps the last taps-1 projected inputs of every scheduled sequence
+//   gate_prep_kernel          silu(q), the bounded forget gate and biases of the gate-tied recurrence, in place
 //   column_scan_kernel        the recurrence of both recurrent mixers, one value column of one head per 8 lanes:
 //                             S <- a S;  [u = beta (v - S^T k)];  S <- S + w u;  o = S^T q, state carried per sequence
 //   head_norm_gate_kernel     per-head RMS norm of the read-out (x weight, x gate), fp32 in place and the bf16 operand
@@ -152,8 +153,9 @@ talk_prep_kernel(float* __restrict__ proj, int ld, const float* __restrict__ bia
 // ---------------------------------------------------------------------------------------------------------------------
 // Attention for all heads of a tile of TQ rows.  A (head, row) pair p = h * TQ + i owns one row of the score tiles and
 // of the running statistics.  Per tile of 64 keys:
-//   A  per key/value head g: the key tile is gathered from the pages into shared memory; raw[p][j] = q_p . k_j for the
-//      pairs of the heads that read g (q carries the score multiplier)
+//   A  per key/value head g: the key tile is gathered from the pages into shared memory (asynchronous copies into one of
+//      two buffers, issued a stage ahead); raw[p][j] = q_p . k_j for the pairs of the heads that read g (q carries the
+//      score multiplier)
 //   B  one warp per pair: mixed[p][j] = sum_g talk[h][g] raw[(g, i)][j], causal mask, online softmax (the running maximum
 //      starts at the sink), weights to shared memory
 //   C  per key/value head g: the value tile is gathered; out[p] += weights[p] . V for the pairs the warp owns (pair
@@ -178,8 +180,8 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     const int D4 = (dim + 3) >> 2, DQ = 4 * D4 + 4, SV = (vdim + 3) & ~3, kv_stride = max(DQ, SV);
     const int n_pairs = H * TQ, rep = H / G;
     float* Qs = sm;                                           // [n_pairs][DQ]
-    float* KVs = Qs + (size_t)n_pairs * DQ;                   // [TK][kv_stride]: a key tile, then a value tile
-    float* Rs = KVs + TK * kv_stride;                         // [n_pairs][TK] raw scores
+    float* KVs = Qs + (size_t)n_pairs * DQ;                   // [2][TK][kv_stride]: key and value tiles, double-buffered
+    float* Rs = KVs + 2 * TK * kv_stride;                     // [n_pairs][TK] raw scores
     float* Ps = Rs + n_pairs * TK;                            // [n_pairs][TK] softmax weights
     float* m_s = Ps + n_pairs * TK;                           // [n_pairs] running maximum
     float* l_s = m_s + n_pairs;                               // [n_pairs] running denominator
@@ -191,7 +193,8 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     pdl_release();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r0 = blockIdx.x * TQ, n_rows = min(TQ, M - r0), S = gridDim.y, sp = blockIdx.y;
+    // later rows see more keys: their tiles start first
+    const int r0 = (gridDim.x - 1 - blockIdx.x) * TQ, n_rows = min(TQ, M - r0), S = gridDim.y, sp = blockIdx.y;
     const bool vec_q = (dim % 4 == 0) && (ld % 4 == 0) && (q_off % 4 == 0), vec_k = dim % 4 == 0, vec_v = vdim % 4 == 0;
 
     if (tid < TQ) {
@@ -218,6 +221,9 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         m_s[p] = (S == 1 && sink) ? sink[p / TQ] : -CUDART_INF_F;
         l_s[p] = 0.f;
     }
+    // value columns of a lane: VW consecutive ones per group of 32 * VW columns (vector loads of the value tile)
+    constexpr int VW = VU >= 4 ? 4 : VU;
+    auto col_of = [&](int u) { return (u / VW) * 32 * VW + lane * VW + (u % VW); };
     float acc[NP][VU];
     int pg[NP];                                               // key/value head of owned pair n (-1: none)
 #pragma unroll
@@ -240,33 +246,58 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
             k_begin = sp * per;
             k_end = min(k_end, k_begin + per);
         }
-        for (int j0 = k_begin; j0 < k_end; j0 += TK) {
-            const int jn = min(TK, k_end - j0);               // keys of this tile
-            // ---- A: raw scores ----
-            for (int g = 0; g < G; ++g) {
-                __syncthreads();                              // the previous tile in KVs is consumed
-                for (int idx = tid; idx < TK * D4; idx += kTalkThreads) {
-                    const int jj = idx / D4, c = (idx - jj * D4) * 4, j = j0 + jj;
+        // A tile of 64 keys is 2 G stages: the key tiles of the G key/value heads (A), then their value tiles (C).  Stage
+        // s lives in buffer s & 1; the gather of stage s + 1 is issued (asynchronous 16-byte copies, zero-filled beyond
+        // the last key) before stage s is computed, so a stage's loads fly during the arithmetic of the one before.
+        const int n_stage = k_begin < k_end ? ((k_end - k_begin + TK - 1) / TK) * 2 * G : 0;
+        auto gather = [&](int stg) {
+            const int tile = stg / (2 * G), ph = stg - tile * 2 * G, j0 = k_begin + tile * TK, jn = min(TK, k_end - j0);
+            const bool is_k = ph < G;
+            const int g = is_k ? ph : ph - G, width = is_k ? dim : vdim, W4 = is_k ? D4 : (SV >> 2);
+            const float* cache = is_k ? kcache : vcache;
+            const bool vec = is_k ? vec_k : vec_v;
+            float* dstb = KVs + (stg & 1) * TK * kv_stride;
+            for (int idx = tid; idx < TK * W4; idx += kTalkThreads) {
+                const int jj = idx / W4, c = (idx - jj * W4) * 4, j = j0 + jj;
+                float* dst = dstb + jj * kv_stride + c;
+                const bool in = jj < jn;
+                const float* src = cache + (in ? (((size_t)pages[j / page_size] * G + g) * page_size + (j % page_size)) * width + c : 0);
+                if (vec) {
+                    const unsigned d32 = (unsigned)__cvta_generic_to_shared(dst);
+                    const int bytes = in ? 16 : 0;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d32), "l"(src), "r"(bytes) : "memory");
+                } else {
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (jj < jn) {
-                        const float* src = kcache + (((size_t)pages[j / page_size] * G + g) * page_size + (j % page_size)) * dim + c;
-                        if (vec_k) v = *reinterpret_cast<const float4*>(src);
-                        else {
-                            v.x = src[0];
-                            if (c + 1 < dim) v.y = src[1];
-                            if (c + 2 < dim) v.z = src[2];
-                            if (c + 3 < dim) v.w = src[3];
-                        }
+                    if (in) {
+                        v.x = src[0];
+                        if (c + 1 < width) v.y = src[1];
+                        if (c + 2 < width) v.z = src[2];
+                        if (c + 3 < width) v.w = src[3];
                     }
-                    *reinterpret_cast<float4*>(KVs + jj * kv_stride + c) = v;
+                    *reinterpret_cast<float4*>(dst) = v;
                 }
-                __syncthreads();
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        if (n_stage > 0) {
+            __syncthreads();                                  // both buffers are free (the previous segment is done)
+            gather(0);
+        }
+        for (int stg = 0; stg < n_stage; ++stg) {
+            const int tile = stg / (2 * G), ph = stg - tile * 2 * G, j0 = k_begin + tile * TK, jn = min(TK, k_end - j0);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();                                  // stage stg has landed; stage stg - 1 is consumed
+            if (stg + 1 < n_stage) gather(stg + 1);
+            const float* KV = KVs + (stg & 1) * TK * kv_stride;
+            if (ph < G) {
+                // ---- A: raw scores of the heads that read key/value head g ----
+                const int g = ph;
                 const int np_g = rep * TQ;
                 const float* Qg = Qs + (size_t)g * np_g * DQ;
                 float* Rg = Rs + g * np_g * TK;
                 if (np_g >= 32) {                             // 4 pairs x 2 keys per thread
-                    const float* k0p = KVs + lane * kv_stride;
-                    const float* k1p = KVs + (lane + 32) * kv_stride;
+                    const float* k0p = KV + lane * kv_stride;
+                    const float* k1p = KV + (lane + 32) * kv_stride;
                     for (int ch = warp; ch * 4 < np_g; ch += kTalkWarps) {
                         const float* qp[4];
 #pragma unroll
@@ -296,7 +327,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                     for (int it = warp; it < 2 * np_g; it += kTalkWarps) {
                         const int lp = it >> 1, jj = lane + 32 * (it & 1);
                         const float* qp = Qg + (size_t)lp * DQ;
-                        const float* kp = KVs + jj * kv_stride;
+                        const float* kp = KV + jj * kv_stride;
                         float a = 0.f;
                         if (jj < jn) {
                             for (int d4 = 0; d4 < D4; ++d4) {
@@ -308,96 +339,88 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                         Rg[lp * TK + jj] = a;
                     }
                 }
-            }
-            __syncthreads();
-            // ---- B: mix across heads, mask, online softmax ----
-            for (int p = warp; p < n_pairs; p += kTalkWarps) {
-                const int h = p / TQ, i = p - h * TQ;
-                const bool live = i >= seg_a && i < seg_b;
-                const int qi = s_pos[i];
-                float s[2];
+                if (ph < G - 1) continue;
+                __syncthreads();                              // the raw scores of all heads are there
+                // ---- B: mix across heads, mask, online softmax ----
+                for (int p = warp; p < n_pairs; p += kTalkWarps) {
+                    const int h = p / TQ, i = p - h * TQ;
+                    const bool live = i >= seg_a && i < seg_b;
+                    const int qi = s_pos[i];
+                    float s[2];
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    const int jj = lane + 32 * t;
-                    const bool ok = live && jj < jn && j0 + jj <= qi;
-                    float v = -CUDART_INF_F;
-                    if (ok) {
-                        if (talk) {
-                            v = 0.f;
-                            for (int g2 = 0; g2 < H; ++g2) v = fmaf(Tm[h * H + g2], Rs[(g2 * TQ + i) * TK + jj], v);
-                        } else {
-                            v = Rs[p * TK + jj];
+                    for (int t = 0; t < 2; ++t) {
+                        const int jj = lane + 32 * t;
+                        const bool ok = live && jj < jn && j0 + jj <= qi;
+                        float v = -CUDART_INF_F;
+                        if (ok) {
+                            if (talk) {
+                                v = 0.f;
+                                for (int g2 = 0; g2 < H; ++g2) v = fmaf(Tm[h * H + g2], Rs[(g2 * TQ + i) * TK + jj], v);
+                            } else {
+                                v = Rs[p * TK + jj];
+                            }
                         }
+                        s[t] = v;
                     }
-                    s[t] = v;
+                    const float m_old = m_s[p];
+                    const float m_new = fmaxf(m_old, warp_max(fmaxf(s[0], s[1])));
+                    float corr = 1.f, p0 = 0.f, p1 = 0.f;
+                    if (m_new != -CUDART_INF_F) {
+                        corr = expf(m_old - m_new);           // exp(-inf) = 0 on the first live tile without a sink
+                        p0 = expf(s[0] - m_new);
+                        p1 = expf(s[1] - m_new);
+                    }
+                    const float psum = warp_sum(p0 + p1);
+                    Ps[p * TK + lane] = p0;
+                    Ps[p * TK + lane + 32] = p1;
+                    if (lane == 0) {
+                        l_s[p] = l_s[p] * corr + psum;
+                        m_s[p] = m_new;
+                        c_s[p] = corr;
+                    }
                 }
-                const float m_old = m_s[p];
-                const float m_new = fmaxf(m_old, warp_max(fmaxf(s[0], s[1])));
-                float corr = 1.f, p0 = 0.f, p1 = 0.f;
-                if (m_new != -CUDART_INF_F) {
-                    corr = expf(m_old - m_new);               // exp(-inf) = 0 on the first live tile without a sink
-                    p0 = expf(s[0] - m_new);
-                    p1 = expf(s[1] - m_new);
-                }
-                const float psum = warp_sum(p0 + p1);
-                Ps[p * TK + lane] = p0;
-                Ps[p * TK + lane + 32] = p1;
-                if (lane == 0) {
-                    l_s[p] = l_s[p] * corr + psum;
-                    m_s[p] = m_new;
-                    c_s[p] = corr;
-                }
+                continue;                                     // the next stage's barrier publishes the weights
             }
-            // ---- C: weighted values ----
+            // ---- C: weighted values of key/value head g ----
+            const int g = ph - G;
             const int jn4 = (jn + 3) & ~3;
-            for (int g = 0; g < G; ++g) {
-                __syncthreads();                              // B is complete / the previous value tile is consumed
-                const int V4 = SV >> 2;
-                for (int idx = tid; idx < TK * V4; idx += kTalkThreads) {
-                    const int jj = idx / V4, c = (idx - jj * V4) * 4, j = j0 + jj;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (jj < jn) {
-                        const float* src = vcache + (((size_t)pages[j / page_size] * G + g) * page_size + (j % page_size)) * vdim + c;
-                        if (vec_v) v = *reinterpret_cast<const float4*>(src);
-                        else {
-                            v.x = src[0];
-                            if (c + 1 < vdim) v.y = src[1];
-                            if (c + 2 < vdim) v.z = src[2];
-                            if (c + 3 < vdim) v.w = src[3];
+#pragma unroll
+            for (int n = 0; n < NP; ++n)
+                if (pg[n] == g) {
+                    const float c = c_s[warp + kTalkWarps * n];
+#pragma unroll
+                    for (int u = 0; u < VU; ++u) acc[n][u] *= c;
+                }
+            for (int j = 0; j < jn4; j += 4) {
+                float v[4][VU];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+                    for (int u = 0; u < VU; u += VW) {
+                        const int col = col_of(u);
+                        const float* src = KV + (j + jj) * kv_stride + col;
+                        if (VW == 4) {
+                            const float4 t = col < SV ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            v[jj][u] = t.x; v[jj][u + 1] = t.y; v[jj][u + 2] = t.z; v[jj][u + 3] = t.w;
+                        } else if (VW == 2) {
+                            const float2 t = col < SV ? *reinterpret_cast<const float2*>(src) : make_float2(0.f, 0.f);
+                            v[jj][u] = t.x; v[jj][u + 1] = t.y;
+                        } else {
+                            v[jj][u] = col < SV ? *src : 0.f;
                         }
                     }
-                    *reinterpret_cast<float4*>(KVs + jj * kv_stride + c) = v;
-                }
-                __syncthreads();
 #pragma unroll
                 for (int n = 0; n < NP; ++n)
                     if (pg[n] == g) {
-                        const float c = c_s[warp + kTalkWarps * n];
-#pragma unroll
-                        for (int u = 0; u < VU; ++u) acc[n][u] *= c;
-                    }
-                for (int j = 0; j < jn4; j += 4) {
-                    float v[4][VU];
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj)
+                        const float4 pj = *reinterpret_cast<const float4*>(Ps + (warp + kTalkWarps * n) * TK + j);
 #pragma unroll
                         for (int u = 0; u < VU; ++u) {
-                            const int col = lane + 32 * u;
-                            v[jj][u] = col < SV ? KVs[(j + jj) * kv_stride + col] : 0.f;
+                            acc[n][u] = fmaf(pj.x, v[0][u], acc[n][u]);
+                            acc[n][u] = fmaf(pj.y, v[1][u], acc[n][u]);
+                            acc[n][u] = fmaf(pj.z, v[2][u], acc[n][u]);
+                            acc[n][u] = fmaf(pj.w, v[3][u], acc[n][u]);
                         }
-#pragma unroll
-                    for (int n = 0; n < NP; ++n)
-                        if (pg[n] == g) {
-                            const float4 pj = *reinterpret_cast<const float4*>(Ps + (warp + kTalkWarps * n) * TK + j);
-#pragma unroll
-                            for (int u = 0; u < VU; ++u) {
-                                acc[n][u] = fmaf(pj.x, v[0][u], acc[n][u]);
-                                acc[n][u] = fmaf(pj.y, v[1][u], acc[n][u]);
-                                acc[n][u] = fmaf(pj.z, v[2][u], acc[n][u]);
-                                acc[n][u] = fmaf(pj.w, v[3][u], acc[n][u]);
-                            }
-                        }
-                }
+                    }
             }
         }
         seg_a = seg_b;
@@ -417,7 +440,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
             const size_t base = (size_t)(r0 + i) * ldo + (size_t)h * vdim;
 #pragma unroll
             for (int u = 0; u < VU; ++u) {
-                const int col = lane + 32 * u;
+                const int col = col_of(u);
                 if (col < vdim) {
                     const float o = acc[n][u] * f;
                     out[base + col] = o;
@@ -437,7 +460,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         if (lane == 0) { dst[0] = m_s[p]; dst[1] = l_s[p]; }
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
-            const int col = lane + 32 * u;
+            const int col = col_of(u);
             if (col < vdim) dst[2 + col] = acc[n][u];
         }
     }
@@ -563,27 +586,44 @@ __global__ void conv_tail_kernel(const float* __restrict__ proj, int ld, int C, 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// q <- silu(q + bias), f <- lower + (1 - lower) sigmoid(f + bias), v <- v + bias in place on the stacked projections of
+// a gate-tied recurrence (one CTA per row): what its scan reads as q, decay and value
+__global__ void gate_prep_kernel(float* __restrict__ proj, int ld, int q_off, int f_off, int v_off, const float* __restrict__ bias,
+                                 const float* __restrict__ lower, int n_qf, int n_v) {
+    pdl_release();
+    pdl_wait();
+    float* row = proj + (size_t)blockIdx.x * ld;
+    for (int c = threadIdx.x; c < n_qf; c += blockDim.x) {
+        row[q_off + c] = siluf_(row[q_off + c] + (bias ? bias[q_off + c] : 0.f));
+        const float lo = lower ? lower[c] : 0.f;
+        row[f_off + c] = fmaf(1.0f - lo, sigmoidf_(row[f_off + c] + (bias ? bias[f_off + c] : 0.f)), lo);
+    }
+    if (bias)
+        for (int c = threadIdx.x; c < n_v; c += blockDim.x) row[v_off + c] += bias[v_off + c];
+}
+
 // The recurrence.  Per head a state S [dim][vdim]; every value column c of S evolves on its own:
 //   S[:, c] <- a_t * S[:, c];   DELTA: u = beta_t (v_t[c] - S[:, c] . k_t), S[:, c] += k_t u;   else: S[:, c] += (1 - a_t) v_t[c]
 //   o_t[c] = S[:, c] . q_t
-// A column lives in the registers of 8 lanes (lane part holds rows part, part + 8, ...); a CTA of 4 warps carries 16
-// columns of one head of one scheduled sequence through the sequence's rows in order, 16 tokens staged in shared memory
-// at a time.  The state is read when the sequence's first row is not position 0, and written back at the end:
-// state[slot][h][c][dim].  Without DELTA the staged inputs are transformed on the way in: q <- silu(q),
-// a <- lower + (1 - lower) sigmoid(a + bias).
+// A column lives in the registers of 8 lanes (lane part holds rows part, part + 8, ...; its dot products are summed in
+// four interleaved partial sums, then across the 8 lanes); a CTA of 4 warps carries 16 columns of one head of one
+// scheduled sequence through the sequence's rows in order, 16 tokens staged in shared memory at a time while the next 16
+// are on their way into registers.  The state is read when the sequence's first row is not position 0, and written
+// back at the end: state[slot][h][c][dim].
 constexpr int kScanThreads = 128, kScanCols = 16, kScanTT = 16;
 
 template <int RP, bool DELTA>
 __global__ void __launch_bounds__(kScanThreads)
-column_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int a_off, int v_off, int beta_off,
-                   const float* __restrict__ in_bias, const float* __restrict__ lower, int H, int G, int dim, int vdim,
-                   float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
-                   const int* __restrict__ seq_count, const int* __restrict__ row_pos, float* __restrict__ o, int ldo) {
+column_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int a_off, int v_off, int beta_off, int H, int G,
+                   int dim, int vdim, float* __restrict__ state, const int* __restrict__ seq_slot,
+                   const int* __restrict__ seq_row0, const int* __restrict__ seq_count, const int* __restrict__ row_pos,
+                   float* __restrict__ o, int ldo) {
     extern __shared__ float sh[];
-    float* sq = sh;                                           // [TT][dim]
-    float* sa = sq + kScanTT * dim;                           // [TT][dim]
-    float* sk = sa + kScanTT * dim;                           // [TT][dim] (DELTA)
-    float* sv = sk + (DELTA ? kScanTT * dim : 0);             // [TT][16]
+    constexpr int DS = 8 * RP;                                // staged row length (channels beyond dim hold zeros)
+    float* sq = sh;                                           // [TT][DS]
+    float* sa = sq + kScanTT * DS;                            // [TT][DS]
+    float* sk = sa + kScanTT * DS;                            // [TT][DS] (DELTA)
+    float* sv = sk + (DELTA ? kScanTT * DS : 0);              // [TT][16]
     float* sb = sv + kScanTT * kScanCols;                     // [TT] (DELTA)
     pdl_release();
     pdl_wait();
@@ -599,70 +639,100 @@ column_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, i
         const int d = part + 8 * r;
         S[r] = (start > 0 && col_ok && d < dim) ? st[d] : 0.f;
     }
+    // Staging: a chunk of 16 tokens is 16 * DS = 128 * RP elements per input; thread tid owns elements tid + 128 i, the
+    // same (token in chunk, channel) for every chunk.
+    int src[RP];                                              // (token in chunk) * ld + channel, -1: a channel beyond dim
+#pragma unroll
+    for (int i = 0; i < RP; ++i) {
+        const int idx = tid + kScanThreads * i, t = idx / DS, d = idx - t * DS;
+        src[i] = d < dim ? t * ld + d : -1;
+    }
+    const int qh = DELTA ? g : h;
+    float rq[RP], ra[RP], rk[DELTA ? RP : 1], rv[2], rb = 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = min(kScanTT, n - t0);
+        const float* base = in + (size_t)(row0 + t0) * ld;
+#pragma unroll
+        for (int i = 0; i < RP; ++i) {
+            const bool ok = src[i] >= 0 && (tid + kScanThreads * i) / DS < nt;
+            rq[i] = ok ? base[src[i] + q_off + qh * dim] : 0.f;
+            ra[i] = ok ? base[src[i] + a_off + h * dim] : 0.f;
+            if (DELTA) rk[i] = ok ? base[src[i] + k_off + g * dim] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = tid + kScanThreads * i, t = idx / kScanCols, c = idx - t * kScanCols;
+            rv[i] = (t < nt && col0 + c < vdim) ? base[(size_t)t * ld + v_off + h * vdim + col0 + c] : 0.f;
+        }
+        if (DELTA && tid < nt) rb = base[(size_t)tid * ld + beta_off + h];
+    };
+    fetch(0);
     for (int t0 = 0; t0 < n; t0 += kScanTT) {
         const int nt = min(kScanTT, n - t0);
-        __syncthreads();
-        for (int idx = tid; idx < nt * dim; idx += kScanThreads) {
-            const int t = idx / dim, d = idx - t * dim;
-            const float* row = in + (size_t)(row0 + t0 + t) * ld;
-            if (DELTA) {
-                sq[idx] = row[q_off + g * dim + d];
-                sk[idx] = row[k_off + g * dim + d];
-                sa[idx] = row[a_off + h * dim + d];
-            } else {
-                sq[idx] = siluf_(row[q_off + h * dim + d] + (in_bias ? in_bias[q_off + h * dim + d] : 0.f));
-                const float lo = lower ? lower[h * dim + d] : 0.f;
-                const float f = row[a_off + h * dim + d] + (in_bias ? in_bias[a_off + h * dim + d] : 0.f);
-                sa[idx] = fmaf(1.0f - lo, sigmoidf_(f), lo);
-            }
-        }
-        for (int idx = tid; idx < nt * kScanCols; idx += kScanThreads) {
-            const int t = idx / kScanCols, c = idx - t * kScanCols;
-            sv[idx] = col0 + c < vdim ? in[(size_t)(row0 + t0 + t) * ld + v_off + h * vdim + col0 + c] +
-                                            ((!DELTA && in_bias) ? in_bias[v_off + h * vdim + col0 + c] : 0.f)
-                                      : 0.f;
-        }
-        if (DELTA)
-            for (int t = tid; t < nt; t += kScanThreads) sb[t] = in[(size_t)(row0 + t0 + t) * ld + beta_off + h];
-        __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float* q = sq + t * dim;
-            const float* a = sa + t * dim;
-            const float v = sv[t * kScanCols + cl];
-            float dot = 0.f;
-            if (DELTA) {
-                const float* k = sk + t * dim;
-                float dk = 0.f;
+        __syncthreads();                                      // the previous chunk is consumed
 #pragma unroll
-                for (int r = 0; r < RP; ++r) {
-                    const int d = part + 8 * r;
-                    if (d < dim) {
-                        S[r] *= a[d];
-                        dk = fmaf(S[r], k[d], dk);
-                    }
+        for (int i = 0; i < RP; ++i) {
+            const int idx = tid + kScanThreads * i;
+            sq[idx] = rq[i];
+            sa[idx] = ra[i];
+            if (DELTA) sk[idx] = rk[i];
+        }
+        sv[tid] = rv[0];
+        sv[tid + kScanThreads] = rv[1];
+        if (DELTA && tid < kScanTT) sb[tid] = rb;
+        __syncthreads();
+        if (t0 + kScanTT < n) fetch(t0 + kScanTT);            // in flight during the recurrence below
+#pragma unroll 4
+        for (int t = 0; t < nt; ++t) {
+            const float* q = sq + t * DS + part;
+            const float* a = sa + t * DS + part;
+            const float v = sv[t * kScanCols + cl];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            if (DELTA) {
+                const float* k = sk + t * DS + part;
+                float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
+#pragma unroll
+                for (int r = 0; r < RP; r += 4) {
+                    S[r] *= a[8 * r];
+                    S[r + 1] *= a[8 * r + 8];
+                    S[r + 2] *= a[8 * r + 16];
+                    S[r + 3] *= a[8 * r + 24];
+                    e0 = fmaf(S[r], k[8 * r], e0);
+                    e1 = fmaf(S[r + 1], k[8 * r + 8], e1);
+                    e2 = fmaf(S[r + 2], k[8 * r + 16], e2);
+                    e3 = fmaf(S[r + 3], k[8 * r + 24], e3);
                 }
+                float dk = (e0 + e1) + (e2 + e3);
                 dk += __shfl_xor_sync(0xffffffffu, dk, 1);
                 dk += __shfl_xor_sync(0xffffffffu, dk, 2);
                 dk += __shfl_xor_sync(0xffffffffu, dk, 4);
                 const float u = sb[t] * (v - dk);
 #pragma unroll
-                for (int r = 0; r < RP; ++r) {
-                    const int d = part + 8 * r;
-                    if (d < dim) {
-                        S[r] = fmaf(k[d], u, S[r]);
-                        dot = fmaf(S[r], q[d], dot);
-                    }
+                for (int r = 0; r < RP; r += 4) {
+                    S[r] = fmaf(k[8 * r], u, S[r]);
+                    S[r + 1] = fmaf(k[8 * r + 8], u, S[r + 1]);
+                    S[r + 2] = fmaf(k[8 * r + 16], u, S[r + 2]);
+                    S[r + 3] = fmaf(k[8 * r + 24], u, S[r + 3]);
+                    d0 = fmaf(S[r], q[8 * r], d0);
+                    d1 = fmaf(S[r + 1], q[8 * r + 8], d1);
+                    d2 = fmaf(S[r + 2], q[8 * r + 16], d2);
+                    d3 = fmaf(S[r + 3], q[8 * r + 24], d3);
                 }
             } else {
 #pragma unroll
-                for (int r = 0; r < RP; ++r) {
-                    const int d = part + 8 * r;
-                    if (d < dim) {
-                        S[r] = fmaf(a[d], S[r], (1.0f - a[d]) * v);
-                        dot = fmaf(S[r], q[d], dot);
-                    }
+                for (int r = 0; r < RP; r += 4) {
+                    const float a0 = a[8 * r], a1 = a[8 * r + 8], a2 = a[8 * r + 16], a3 = a[8 * r + 24];
+                    S[r] = fmaf(a0, S[r], (1.0f - a0) * v);
+                    S[r + 1] = fmaf(a1, S[r + 1], (1.0f - a1) * v);
+                    S[r + 2] = fmaf(a2, S[r + 2], (1.0f - a2) * v);
+                    S[r + 3] = fmaf(a3, S[r + 3], (1.0f - a3) * v);
+                    d0 = fmaf(S[r], q[8 * r], d0);
+                    d1 = fmaf(S[r + 1], q[8 * r + 8], d1);
+                    d2 = fmaf(S[r + 2], q[8 * r + 16], d2);
+                    d3 = fmaf(S[r + 3], q[8 * r + 24], d3);
                 }
             }
+            float dot = (d0 + d1) + (d2 + d3);
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
             dot += __shfl_xor_sync(0xffffffffu, dot, 4);
@@ -733,7 +803,7 @@ cudaError_t launch_talk_prep(float* proj, int ld, const float* bias, int q_off, 
 
 static size_t talk_smem(const TalkShape& a, int TQ) {
     const int D4 = (a.dim + 3) / 4, DQ = 4 * D4 + 4, SV = (a.vdim + 3) & ~3, kvs = std::max(DQ, SV), np = a.heads * TQ;
-    return ((size_t)np * DQ + (size_t)kTalkTK * kvs + 2 * (size_t)np * kTalkTK + 3 * (size_t)np + (size_t)a.heads * a.heads) * 4 +
+    return ((size_t)np * DQ + 2 * (size_t)kTalkTK * kvs + 2 * (size_t)np * kTalkTK + 3 * (size_t)np + (size_t)a.heads * a.heads) * 4 +
            2 * (size_t)TQ * 4;
 }
 
@@ -815,17 +885,22 @@ cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* 
 template <int RP, bool DELTA>
 static cudaError_t launch_scan_inst(const float* in, int ld, const ScanInputs& si, int H, int G, int dim, int vdim, float* state,
                                     const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st) {
-    const size_t smem = (size_t)((DELTA ? 3 : 2) * kScanTT * dim + kScanTT * kScanCols + kScanTT) * 4;
+    const size_t smem = (size_t)((DELTA ? 3 : 2) * kScanTT * 8 * RP + kScanTT * kScanCols + kScanTT) * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(column_scan_kernel<RP, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
     return launch_pdl(column_scan_kernel<RP, DELTA>, dim3(n_seq, H, (vdim + kScanCols - 1) / kScanCols), dim3(kScanThreads), smem, st,
-                      in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, si.in_bias, si.lower, H, G, dim, vdim, state,
-                      sm.slot, sm.row0, sm.count, rm.pos, o, ldo);
+                      in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, G, dim, vdim, state, sm.slot, sm.row0,
+                      sm.count, rm.pos, o, ldo);
 }
 
-// delta: the delta rule (reads k and beta); otherwise the gate-tied write with the input transforms of ScanInputs
+cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_off, const float* bias, const float* lower, int n_qf,
+                             int n_v, int M, cudaStream_t st) {
+    return launch_pdl(gate_prep_kernel, dim3(M), dim3(256), 0, st, proj, ld, q_off, f_off, v_off, bias, lower, n_qf, n_v);
+}
+
+// delta: the delta rule (reads k and beta); otherwise the gate-tied write (its inputs prepared by launch_gate_prep)
 cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
                                float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
                                cudaStream_t st) {
