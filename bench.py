@@ -5,8 +5,8 @@
 
 Workload (BASELINE.json configs[1]): Dia-1.6B, bf16 weights, ONE transcript, CFG batch 2, a full
 3072-token generation = 3071 autoregressive decode steps.  A bench "step" is one such generation.
-With N > 1 GPUs every rank runs its own utterance (replicas, no collective on the data path:
-SURVEY.md 8(e)); `value` is the sum over ranks divided by the slowest rank's time (weak scaling).
+With N > 1 GPUs every rank runs its own utterance (replicas, no collective on the data
+path); `value` is the sum over ranks divided by the slowest rank's time (weak scaling).
 
   value  frames/s of the decode loop with everything already resident in HBM (encoder output,
          cross-KV, token grid), timed on the device with CUDA events on the launching stream.
@@ -71,7 +71,7 @@ def workload_config(text_len: int, world: int, variant: str = "dense", amount: f
 
 def algorithmic_bytes(cfg, slot: int, text_len: int, kv_elem: int = 4, n_hidden: int | None = None,
                       weight_scale: float = 1.0, dense_bytes: int | None = None) -> int:
-    """bf16 weights of the 18 layers + logits head, fp32 norm weights, 9 embedding rows,
+    """Bytes one decode step must move: bf16 weights of the 18 layers + logits head, fp32 norm weights, 9 embedding rows,
     plus self-KV rows read / appended and the valid cross-KV rows of the conditional row.  Pruned variants:
     ``n_hidden`` = live MLP width of a structurally pruned model; ``weight_scale`` = 0.5625 for 2:4 (half the
     values + 2 bits of metadata per kept value)."""
@@ -148,7 +148,7 @@ def build_cpu_model(seed: int, suppress_eos: bool):
     SY.init_synthetic_(dia.model.named_parameters(), seed)
     if suppress_eos:
         # random weights would emit EOS on channel 0 within ~1000 steps and end the utterance early;
-        # a zero EOS column keeps all 3071 steps running (SURVEY.md 8(d))
+        # a zero EOS column keeps all 3071 steps running
         with torch.no_grad():
             dia.model.decoder.logits_dense.weight[:, 0, cfg.data.audio_eos_value] = 0.0
     return dia, cfg
@@ -415,7 +415,7 @@ def run_ours(args) -> None:
 def batch_workload(dia, cfg, texts, max_tokens: int, per_launch: int, dev) -> dict:
     """BASELINE.json configs[4] on ONE rank: its share of the transcripts through ``Dia.generate_batch`` (``per_launch``
     utterances per kernel launch: 2N rows share one pass over the weights), host text in, host codes out.  Returns frames,
-    wall seconds and the roofline of this shape (SURVEY.md 8(d): bytes = W + N * 36 864 * e * (t + 2 Lt) per step of N
+    wall seconds and the roofline of this shape (bytes = W + N * 36 864 * e * (t + 2 Lt) per step of N
     frames)."""
     import torch
     torch.cuda.synchronize(dev)

@@ -127,7 +127,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
 
 
 def check(rc: int, what: str = "") -> None:
-    """Non-zero ABI codes become exceptions (the reference raises from Python; SURVEY.md 8(b))."""
+    """Non-zero ABI codes become exceptions (the reference raises from Python)."""
     if rc == 0:
         return
     lib = load()

@@ -105,7 +105,7 @@ class DiaConfig(BaseModel, frozen=True):
 
 
 def dia_1_6b_config() -> DiaConfig:
-    """The public nari-labs/Dia-1.6B configuration (SURVEY.md Appendix A)."""
+    """The public nari-labs/Dia-1.6B configuration."""
     return DiaConfig(
         model=ModelConfig(
             encoder=EncoderConfig(n_layer=12, n_embd=1024, n_hidden=4096, n_head=16, head_dim=128),

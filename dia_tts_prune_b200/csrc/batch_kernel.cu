@@ -1,4 +1,4 @@
-// batch_kernel.cu - the persistent decode-step kernel for N utterances per GPU (SURVEY.md 8(f) rank 2).
+// batch_kernel.cu - the persistent decode-step kernel for N utterances per GPU.
 //
 // Same dataflow as step_kernel.cu - one CTA per SM, a producer warp streaming this CTA's weight slabs through a
 // shared-memory ring with 1-D bulk copies, flag-in-data vectors between CTAs, no grid barrier, the loop of

@@ -1,10 +1,10 @@
 // gemm_tcgen05.cu - the dense contractions OFF the decode step (encoder, cross-attention K/V precompute, prompt
-// prefill: SURVEY.md 8(f) rank 1) on the 5th-generation tensor cores.
+// prefill) on the 5th-generation tensor cores.
 //
 //   Y[M][N] (fp32) = X[M][K] (fp32) . W[K][N] (bf16)           DenseGeneral.forward, dia/layers.py:55-66, M = B*T rows
 //
 // The reference runs these in fp32 and the K/V a prefill writes are re-read by every later greedy step, so the
-// activations may not be rounded to bf16 (hard part 2).  X is therefore split into three bf16 terms
+// activations may not be rounded to bf16.  X is therefore split into three bf16 terms
 // (x = hi + lo + lo2, exact to 24 bits) and each k-step issues three tcgen05.mma into the SAME fp32 accumulator in
 // tensor memory: the product has fp32-operand accuracy at bf16 tensor-core speed.
 //

@@ -24,7 +24,7 @@
 //   h = layernorm(x)                            layernorm_rows
 //   proj = h W_in^T                             linear: every projection of the mixer and the feed-forward's up rows
 //   mixer on proj -> out[:, :mixer columns]     talk_prep + talk_attention | gate_prep + column_scan + head_norm_gate |
-//                                               delta_prep + conv_tail + column_scan + head_norm_gate
+//                                               linear x 2 (decay, gate) + delta_prep + conv_tail + column_scan + head_norm_gate
 //   out[:, mixer columns:] = act(proj up rows)  xielu_rows
 //   x += out W_out^T                            linear with the residual add (W_out = [W_o | W_down])
 //
@@ -379,13 +379,16 @@ int mixer_kernels(lm_b200_engine* e, const lm_b200_layer& l, const InCols& c, fl
             break;
         }
         case LM_B200_MIXER_CHANNEL_DELTA: {
-            const lm::DeltaShape d{l.heads, l.kv_heads, l.dim, l.vdim, l.conv_taps, l.rank_a, l.rank_g, l.unit_eps, l.conv_w,
-                                   l.a_log, l.dt_bias, l.w_a2, l.w_g2};
+            const lm::DeltaShape d{l.heads, l.kv_heads, l.dim, l.vdim, l.conv_taps, l.unit_eps, l.conv_w, l.a_log, l.dt_bias};
             const int ldr = rec_cols(l), C = 2 * l.kv_heads * l.dim + l.heads * l.vdim;
-            LCK(lm::launch_delta_prep(proj, c.n, c.beta, c.a1, c.g1, d, l.conv_tail, v.rm, e->rec, ldr, M, st));
-            LCK(lm::launch_conv_tail(proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
             const int k0 = l.kv_heads * l.dim, v0 = 2 * k0, d0 = v0 + l.heads * l.vdim, g0 = d0 + l.heads * l.dim,
                       b0 = g0 + l.heads * l.vdim;
+            // the second steps of the decay and gate projections: fp32 products (they enter the recurrence), straight into
+            // the decay and gate columns of the recurrence inputs
+            LCK(lm::launch_linear(proj + c.a1, c.n, l.w_a2, 0, e->rec + d0, ldr, M, l.heads * l.dim, l.rank_a, nullptr, st));
+            LCK(lm::launch_linear(proj + c.g1, c.n, l.w_g2, 0, e->rec + g0, ldr, M, l.heads * l.vdim, l.rank_g, nullptr, st));
+            LCK(lm::launch_delta_prep(proj, c.n, c.beta, d, l.conv_tail, v.rm, e->rec, ldr, M, st));
+            LCK(lm::launch_conv_tail(proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
             const lm::ScanInputs si{0, k0, d0, v0, b0};
             LCK(lm::launch_column_scan(e->rec, ldr, si, true, l.heads, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
                                        e->outcat, ko, st));

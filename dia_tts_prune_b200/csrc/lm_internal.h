@@ -78,9 +78,9 @@ struct TalkShape {
     const float* talk; const float* sink;                                       // [heads][heads], [heads]; each may be null
 };
 struct DeltaShape {
-    int heads, kv_heads, dim, vdim, taps, rank_a, rank_g;
+    int heads, kv_heads, dim, vdim, taps;
     float unit_eps;
-    const float* conv_w; const float* a_log; const float* dt_bias; const float* w_a2; const float* w_g2;
+    const float* conv_w; const float* a_log; const float* dt_bias;
 };
 // columns of the recurrence's inputs in their row
 struct ScanInputs { int q_off, k_off, a_off, v_off, beta_off; };
@@ -98,8 +98,8 @@ bool talk_attention_supported(const TalkShape& a);
 cudaError_t launch_talk_attention(const float* proj, int ld, int q_off, int gate_off, const float* kcache, const float* vcache,
                                   const PageMap& pm, const TalkShape& a, const RowMeta& rm, float* out, int ldo, void* out_bf16,
                                   float* split_ws, unsigned* arrived, int M, cudaStream_t st);
-cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, int a1_off, int g1_off, const DeltaShape& d,
-                              const float* tail, const RowMeta& rm, float* rec, int ldr, int M, cudaStream_t st);
+cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, const DeltaShape& d, const float* tail, const RowMeta& rm,
+                              float* rec, int ldr, int M, cudaStream_t st);
 cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* tail, const SeqMeta& sm, int n_seq,
                              cudaStream_t st);
 cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_off, const float* bias, const float* lower, int n_qf,

@@ -505,15 +505,15 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 // One CTA per row.  Channels c of [q | k | v] (C = 2 G dim + H vdim, the first columns of the stacked projections):
 //   conv_c = silu(sum_o cw[c][taps-1-o] * u_c(pos - o)),  u from the step's earlier rows or the sequence's tail, zero
 //   before position 0;  q, k heads -> unit vectors (q also x dim^-1/2);  beta = sigmoid;  decay[h][d] =
-//   exp(-exp(a_log[h]) softplus(a2[h d] . a1 + dt_bias[h d]));  gate[h][c] = sigmoid(g2[h c] . g1).
+//   exp(-exp(a_log[h]) softplus(z[h d] + dt_bias[h d]));  gate[h][c] = sigmoid(y[h c]), where z and y - the second steps
+//   of the two-step decay and gate projections, fp32 products - already stand in the row's decay and gate columns.
 // rec row: q (G dim) | k (G dim) | v (H vdim) | decay (H dim) | gate (H vdim) | beta (H)
 __global__ void __launch_bounds__(256)
-delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int a1_off, int g1_off, int H, int G, int dim, int vdim,
-                  int taps, int ra, int rg, const float* __restrict__ cw, const float* __restrict__ tail,
-                  const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ w_a2,
-                  const float* __restrict__ w_g2, float unit_eps, const int* __restrict__ row_slot,
+delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int H, int G, int dim, int vdim, int taps,
+                  const float* __restrict__ cw, const float* __restrict__ tail, const float* __restrict__ a_log,
+                  const float* __restrict__ dt_bias, float unit_eps, const int* __restrict__ row_slot,
                   const int* __restrict__ row_pos, const int* __restrict__ row_start, float* __restrict__ rec, int ldr) {
-    extern __shared__ float cbuf[];                           // [C] convolved + silu, then [ra + rg] inner projections
+    extern __shared__ float cbuf[];                           // [C] convolved + silu
     pdl_release();
     pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
@@ -521,7 +521,6 @@ delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int a1_o
     const int slot = row_slot[r], pos = row_pos[r], start = row_start[r];
     const float* row = proj + (size_t)r * ld;
     float* dst = rec + (size_t)r * ldr;
-    float* inner = cbuf + C;
     for (int c = tid; c < C; c += blockDim.x) {
         float acc = 0.f;
         for (int o = 0; o < taps; ++o) {
@@ -533,7 +532,6 @@ delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int a1_o
         }
         cbuf[c] = siluf_(acc);
     }
-    for (int i = tid; i < ra + rg; i += blockDim.x) inner[i] = row[i < ra ? a1_off + i : g1_off + (i - ra)];
     __syncthreads();
     const float qmul = 1.0f / sqrtf((float)dim);
     for (int hh = warp; hh < 2 * G; hh += nwarp) {            // q heads, then k heads
@@ -547,15 +545,10 @@ delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int a1_o
     const int v0 = 2 * G * dim, d0 = v0 + H * vdim, g0 = d0 + H * dim, b0 = g0 + H * vdim;
     for (int c = tid; c < H * vdim; c += blockDim.x) {
         dst[v0 + c] = cbuf[v0 + c];
-        float z = 0.f;
-        for (int i = 0; i < rg; ++i) z = fmaf(w_g2[(size_t)c * rg + i], inner[ra + i], z);
-        dst[g0 + c] = sigmoidf_(z);
+        dst[g0 + c] = sigmoidf_(dst[g0 + c]);                  // the second step of the gate projection is already there
     }
-    for (int c = tid; c < H * dim; c += blockDim.x) {
-        float z = dt_bias[c];
-        for (int i = 0; i < ra; ++i) z = fmaf(w_a2[(size_t)c * ra + i], inner[i], z);
-        dst[d0 + c] = expf(-expf(a_log[c / dim]) * softplusf_(z));
-    }
+    for (int c = tid; c < H * dim; c += blockDim.x)            // ... and that of the decay projection
+        dst[d0 + c] = expf(-expf(a_log[c / dim]) * softplusf_(dst[d0 + c] + dt_bias[c]));
     for (int h = tid; h < H; h += blockDim.x) dst[b0 + h] = sigmoidf_(row[beta_off + h]);
 }
 
@@ -861,18 +854,17 @@ cudaError_t launch_talk_attention(const float* proj, int ld, int q_off, int gate
 #undef TALK_CASE
 }
 
-cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, int a1_off, int g1_off, const DeltaShape& d,
-                              const float* tail, const RowMeta& rm, float* rec, int ldr, int M, cudaStream_t st) {
+cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, const DeltaShape& d, const float* tail, const RowMeta& rm,
+                              float* rec, int ldr, int M, cudaStream_t st) {
     if (d.taps < 1 || d.taps > kMaxTaps) return cudaErrorNotSupported;
     const int C = 2 * d.kv_heads * d.dim + d.heads * d.vdim;
-    const size_t smem = (size_t)(C + d.rank_a + d.rank_g) * 4;
+    const size_t smem = (size_t)C * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(delta_prep_kernel, dim3(M), dim3(256), smem, st, proj, ld, beta_off, a1_off, g1_off, d.heads, d.kv_heads,
-                      d.dim, d.vdim, d.taps, d.rank_a, d.rank_g, d.conv_w, tail, d.a_log, d.dt_bias, d.w_a2, d.w_g2, d.unit_eps,
-                      rm.slot, rm.pos, rm.start, rec, ldr);
+    return launch_pdl(delta_prep_kernel, dim3(M), dim3(256), smem, st, proj, ld, beta_off, d.heads, d.kv_heads, d.dim, d.vdim, d.taps,
+                      d.conv_w, tail, d.a_log, d.dt_bias, d.unit_eps, rm.slot, rm.pos, rm.start, rec, ldr);
 }
 
 cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* tail, const SeqMeta& sm, int n_seq,

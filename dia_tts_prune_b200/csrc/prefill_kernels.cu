@@ -1,5 +1,5 @@
 // prefill_kernels.cu - everything around the tcgen05 GEMMs of the T > 1 passes (encoder, cross-attention K/V
-// precompute, prompt prefill: SURVEY.md 8(f) rank 1) that is not a dense contraction:
+// precompute, prompt prefill) that is not a dense contraction:
 //
 //   attention_rows_kernel   F.scaled_dot_product_attention call sites (dia/layers.py:329-337) for T > 1: causal GQA
 //                           self-attention of the prompt prefill, full / pad-partitioned encoder self-attention,
@@ -37,7 +37,7 @@ constexpr int kAttnSmem = (kAQ * kQStride + kAK * kQStride + kAK * kHeadDim + kA
 
 // mode 0: causal - query t attends keys [0, t]                               (prompt prefill, dia/layers.py:722-766)
 // mode 1: partition - query t < n attends keys [0, n), t >= n keys [n, Tk)   (encoder mask, dia/state.py:24-31)
-// mode 2: prefix - every query attends keys [0, n); n == 0 gives exact zeros (cross-attention, SURVEY Appendix C Q7)
+// mode 2: prefix - every query attends keys [0, n); n == 0 gives exact zeros (cross-attention)
 // n = n_valid[b].  q / out: [B][Tq][Hq][128]; k / v: [B][Hkv][Tk_stride][128]; query head h reads kv head h / (Hq / Hkv).
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_rows_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,

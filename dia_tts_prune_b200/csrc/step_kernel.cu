@@ -22,7 +22,7 @@
 //    one column partition, so each element of x lives in a register of the thread that owns its column;
 //  * 8 math warps consume ring slots (one slot per warp at a time) on the tensor cores (mma.sync
 //    m16n8k16, swap-AB: 16 output columns x the 2 batch rows split into three bf16 terms, exact to
-//    24 bits, so the product has fp32-activation accuracy - SURVEY.md 8(c)); residual stream, norms,
+//    24 bits, so the product has fp32-activation accuracy); residual stream, norms,
 //    softmax and the KV cache stay fp32, reductions run in a fixed order (deterministic).  2:4-pruned
 //    checkpoints stream compressed slabs (2 of every 4 K entries + metadata, 0.5625 of the bytes) and
 //    use mma.sp m16n8k32 on the same operand plumbing;

@@ -11,14 +11,14 @@ What runs where
     entirely in the hand-written sm_100a kernels of ``csrc/`` through the C ABI (``engine.py``).
     There is no eager fallback for them: without a CUDA device they raise.
   * ``Encoder``, ``Decoder.precompute_cross_attn_cache`` and the prompt prefill (``Decoder.forward``)
-    are once-per-utterance work (SURVEY.md 8(f) rank 1).  Every dense layer of these T > 1 passes runs on
+    are once-per-utterance work.  Every dense layer of these T > 1 passes runs on
     the tcgen05 / TMEM GEMM of ``csrc/gemm_tcgen05.cu`` (``DenseGeneral._forward_tcgen05``); their attention is
     library SDPA in fp32.  The results feed the decode kernels through the KV caches.
   * Pruned checkpoints: ``Decoder.engine()`` drops exactly-dead MLP neurons from the weight stream and streams a
     2:4 model compressed on ``mma.sp`` (``pruning_utils``).
 
 Numerics: dense kernels may be stored bf16 (``compute_dtype``), but activations, residual stream,
-norms, softmax and KV caches are always fp32 (SURVEY.md 8(c)).
+norms, softmax and KV caches are always fp32.
 """
 
 from __future__ import annotations
@@ -197,7 +197,7 @@ class MlpBlock(nn.Module):
 
 class RotaryEmbedding(nn.Module):
     """Half-split RoPE, theta = position * max_timescale^(-2i/d) (intended semantics of
-    dia/layers.py:126-173; the shipped forward has a shape bug, SURVEY.md Appendix B1)."""
+    dia/layers.py:126-173; the shipped forward has a shape bug)."""
 
     def __init__(self, embedding_dims: int, min_timescale: int = 1, max_timescale: int = 10000,
                  dtype: torch.dtype = torch.float32):
@@ -262,7 +262,7 @@ class Attention(nn.Module):
                                              is_causal=is_causal and not self.is_cross_attn, dropout_p=0.0)
         if attn_mask is not None and attn_mask.dtype == torch.bool:
             # a query with no allowed key contributes exact zeros (the reference's CPU SDPA behaviour,
-            # SURVEY.md Appendix C Q7) - made explicit because GPU SDPA backends may return NaN there
+            # made explicit here because GPU SDPA backends may return NaN there
             out = torch.where(attn_mask.any(dim=-1, keepdim=True), out, torch.zeros((), dtype=out.dtype, device=out.device))
         return self.o_proj(out.transpose(1, 2).contiguous()).to(Xq.dtype)
 
@@ -592,8 +592,7 @@ class Decoder(nn.Module):
         """Same caches as ``precompute_cross_attn_cache`` for the entries that are ever observed.  ``enc_live`` is
         the encoder output of the valid text bytes of the conditional row, ``[1, n, E]``.  The reference projects
         all 2 x text_length encoder positions in every layer, but the unconditional row is fully masked and so are
-        the pad positions of the conditional row (overwriting them with noise leaves the
-        logits bit-identical); here those entries are zeros and only ``n`` rows are projected."""
+        the pad positions of the conditional row; here those entries are zeros and only ``n`` rows are projected."""
         out: list[KVCache] = []
         n = enc_live.shape[1]
         if enc_live.is_cuda and not torch.is_grad_enabled():

@@ -243,7 +243,7 @@ class ChannelDelta:
         self.w_o = w_o
         self.conv_w = _f32(torch.cat([conv_q, conv_k, conv_v], dim=0), device)
         self.a_log, self.dt_bias = _f32(a_log, device), _f32(dt_bias, device)
-        self.w_a2, self.w_g2 = _f32(w_a2, device), _f32(w_g2, device)
+        self.w_a2, self.w_g2 = _bf16(w_a2, device), _bf16(w_g2, device)
         self.head_norm = _f32(head_norm, device)
         self.unit_eps = float(unit_eps)
 

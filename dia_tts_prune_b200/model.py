@@ -12,7 +12,7 @@ the BOS-masked write-back - so a run of decode steps costs one kernel launch and
 ``_decoder_step`` remains available as the single-step boundary.
 
 Declared deviations from the reference (all in its favour or outside the kernel scope):
-  * the shipped loop raises before the first token (SURVEY.md Appendix B); the intended semantics,
+  * the shipped loop raises before the first token; the intended semantics,
     including every quirk of Appendix C, are implemented;
   * DAC (third-party codec) is loaded lazily and only if installed; ``generate(..., output="codes")``
     returns the DAC-ready code tensor without it;
@@ -184,7 +184,7 @@ class Dia:
             prefill_step += audio_prompt.shape[0]
             rows.append(audio_prompt.to(device=self.device, dtype=torch.int32))
         # the delay tail is PAD, not -1 (dia/model.py:330-333) - which is why the first 14 predictions
-        # after a prompt are discarded by the masked write-back (SURVEY.md Appendix C, Q3)
+        # after a prompt are discarded by the masked write-back
         rows.append(torch.full((max(dt.delay_pattern), dt.channels), dt.audio_pad_value, dtype=torch.int32,
                                device=self.device))
         grid = torch.cat(rows, dim=0)
@@ -209,7 +209,7 @@ class Dia:
                 raise NotImplementedError("text with embedded pad bytes is not supported by the cross-attention kernel")
             if self.live_text_only and n_valid > 0:
                 # Only the n_valid text bytes of the conditional row are ever observed by the decoder: the
-                # unconditional row and the pad positions are masked everywhere (SURVEY.md Appendix C Q7), and the
+                # unconditional row and the pad positions are masked everywhere, and the
                 # encoder never mixes pad and non-pad tokens (dia/state.py:24-31).  Encode and project just those.
                 live = cond[:, :n_valid]
                 es_live = EncoderInferenceState(
@@ -390,7 +390,7 @@ class Dia:
             print(f"Error during final decoding: {e}")
             return None
 
-    # ---- N utterances per launch (SURVEY.md 8(f) rank 2; no counterpart in the reference, whose batch is the CFG pair) ----
+    # ---- N utterances per launch (no counterpart in the reference, whose batch is the CFG pair) ----
     @torch.inference_mode()
     def generate_batch(self, texts: list[str], max_tokens: int | None = None, cfg_scale: float = 3.0,
                        temperature: float = 1.3, top_p: float = 0.95, cfg_filter_top_k: int | None = 35,

@@ -1,8 +1,7 @@
 """Weight producers for the pruned variants (drop-in for the reference's ``dia/pruning_utils.py``).
 
 Thin wrappers over ``torch.nn.utils.prune`` applied to every ``DenseGeneral`` - masks only, shapes
-never change (dia/pruning_utils.py:13-179) - plus the 2:4 mask the reference does not have
-(SURVEY.md 8(d), config 4).  After ``make_pruning_permanent`` the Decoder's repacked weight copy is invalidated and rebuilt on the next
+never change (dia/pruning_utils.py:13-179) - plus the 2:4 mask the reference does not have.  After ``make_pruning_permanent`` the Decoder's repacked weight copy is invalidated and rebuilt on the next
 decode call.  The rebuild physically drops MLP hidden neurons whose contribution is exactly zero
 (:func:`plan_mlp_compaction` - the "reduced MLP width" of a ``--prune-dim 0`` checkpoint, offline_prune.py:43):
 the decode kernels then stream (and the roofline counts) only the live part of ``wi_fused`` / ``wo``.  Other
@@ -72,7 +71,7 @@ def mask_2to4(w: torch.Tensor, K: int) -> torch.Tensor:
 @torch.no_grad()
 def apply_2to4_pruning(model: nn.Module, module_types=DEFAULT_PRUNABLE_MODULES):
     """Keep the 2 largest-magnitude of every 4 consecutive K (input) entries per output column of each
-    kernel viewed as [K, N] (SURVEY.md 8(d) config 4 (ii)); applied as a custom mask so that
+    kernel viewed as [K, N]; applied as a custom mask so that
     ``make_pruning_permanent`` / ``check_pruning_sparsity`` treat it like the other modes."""
     for m, name in get_prunable_modules(model, module_types):
         w = getattr(m, name)

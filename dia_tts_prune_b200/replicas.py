@@ -1,4 +1,4 @@
-"""Multi-GPU = replicas over independent utterances (SURVEY.md 8(e)): one process per GPU, utterance
+"""Multi-GPU = replicas over independent utterances: one process per GPU, utterance
 i goes to rank i % world, no collective on the data path.  The only communication is the end-of-run
 reduction of (frames, seconds) used for the throughput line, over NCCL on GPUs or gloo on CPU."""
 

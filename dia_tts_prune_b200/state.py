@@ -3,12 +3,12 @@
 Same class names, constructor arguments and fields as the reference
 (``create_attn_mask`` dia/state.py:8-39, ``EncoderInferenceState`` :42-69, ``KVCache`` :72-109,
 ``DecoderInferenceState`` :112-169, ``DecoderOutput`` :172-208), with the intended behaviour where
-the shipped code is broken (SURVEY.md Appendix B): ``KVCache.prefill`` returns ``(k, v)`` and
+the shipped code is broken: ``KVCache.prefill`` returns ``(k, v)`` and
 ``DecoderOutput.get_tokens_at(step)`` returns the 1-D row.
 
 The decode kernels read and write ``KVCache.k`` / ``KVCache.v`` in place through their data
 pointers, so those stay ordinary ``[2, heads, max_len, 128]`` tensors the caller can index.
-Self caches are always float32 (SURVEY.md 8(c): a bf16 cache cannot meet the parity bar).
+Self caches are always float32 (a bf16 cache cannot meet the parity bar).
 """
 
 from __future__ import annotations
@@ -82,7 +82,7 @@ class KVCache:
 
     def prefill(self, k: torch.Tensor, v: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         """Write slots [0, n) and leave ``current_idx = n - 1`` - the reference's value, which makes
-        the first decode step overwrite the last prefilled slot (SURVEY.md Appendix C, Q2)."""
+        the first decode step overwrite the last prefilled slot."""
         n = k.shape[2]
         self.k[:, :, :n, :] = k
         self.v[:, :, :n, :] = v

@@ -1,6 +1,6 @@
 """Seeded synthetic weights and transcripts (there is no network for checkpoints).
 
-The weight recipe is the one SURVEY.md section 8(d) fixes, shared by the oracle runs
+The weight recipe is fixed here and shared by the oracle runs
 that produced tests/golden/ and by every GPU test / bench run: iterate the
 parameters in ``named_parameters()`` order with ONE seeded CPU generator,
 RMSNorm weights = 1, embeddings ~ N(0,1), dense kernels ~ N(0, fan_in^-1/2),

@@ -74,7 +74,7 @@ typedef struct dia_b200_gen_params {
     int32_t max_tokens;     /* loop bound, dia/model.py:702,748 */
     int32_t prefill_step;   /* DecoderOutput.prefill_step, dia/state.py:205-208 */
     int32_t first_slot;     /* KVCache.current_idx when the loop starts: 0 without an audio prompt,
-                               prefill_step-2 after a prefill (dia/state.py:105-109; SURVEY.md App. C Q2) */
+                               prefill_step-2 after a prefill (dia/state.py:105-109) */
     int32_t reserved;
     uint64_t seed;          /* Philox key for the multinomial draw */
 } dia_b200_gen_params;
@@ -110,7 +110,7 @@ int64_t dia_b200_engine_weight_stream_bytes(const dia_b200_engine *e);
 
 /* Repack the decoder parameters into the per-CTA bf16 stream the step kernel reads.
  * `tensors` is a HOST array of DEVICE pointers in this order (state_dict names of
- * dia/layers.py, SURVEY.md Appendix A):
+ * dia/layers.py):
  *   [0 .. C)                       decoder.embeddings.c.weight            (V, D)   always float32
  *   then per layer l, 11 tensors:  pre_sa_norm, pre_ca_norm, pre_mlp_norm (D,)     always float32
  *                                  self_attention.{q,k,v,o}_proj.weight
@@ -139,7 +139,7 @@ int dia_b200_set_rope_table(dia_b200_engine *e, const float *sin_host, const flo
 /* Bind one utterance's caches: HOST arrays (n_layer entries) of DEVICE pointers.
  * Replaces DecoderInferenceState.self_attn_cache / cross_attn_cache (dia/state.py:112-162).
  * text_len = number of leading valid (non-pad) text positions of the conditional row; the
- * unconditional row attends nothing and contributes exact zeros (SURVEY.md Appendix C Q7). */
+ * unconditional row attends nothing and contributes exact zeros. */
 int dia_b200_bind_caches(dia_b200_engine *e, void *const *self_k, void *const *self_v,
                          const void *const *cross_k, const void *const *cross_v, int n_layer, int text_len,
                          void *stream);
@@ -193,7 +193,7 @@ int dia_b200_build_delay_indices(int32_t *t_idx, int64_t *indices, int B, int T,
 int dia_b200_build_revert_indices(int64_t *t_idx, int64_t *indices, int B, int T, int C, const int32_t *delay_host,
                                   void *stream);
 
-/* ---- N utterances per GPU in one launch (SURVEY.md 8(f) rank 2) ------------------------------------------------
+/* ---- N utterances per GPU in one launch ------------------------------------------------
  * The reference hard-wires the CFG batch of 2 rows (dia/state.py:58-60,83-84,138-139); a batched engine decodes up to
  * DIA_B200_MAX_UTTERANCES independent utterances per launch - 2N batch rows share ONE pass over the weights (tcgen05
  * tensor cores, accumulators in tensor memory).  Every utterance keeps the reference's own state objects: its own

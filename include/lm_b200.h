@@ -98,7 +98,7 @@ typedef struct lm_b200_layer {
     const float *lower;            /* [heads*dim] lower bound of the forget gate (HGRN2) */
     const float *conv_w;           /* [2 kv_heads*dim + heads*vdim][conv_taps]: q, k, v channels; the last tap is the current token's */
     const float *a_log, *dt_bias;  /* [heads], [heads*dim]: decay = exp(-exp(a_log_h) softplus(a2 a1 h + dt_bias)) */
-    const float *w_a2, *w_g2;      /* [heads*dim][rank_a], [heads*vdim][rank_g] second steps of the decay and gate projections */
+    const void *w_a2, *w_g2;       /* bf16 [heads*dim][rank_a], [heads*vdim][rank_g]: second steps of the decay and gate projections (fp32 arithmetic) */
     float *rec_state;              /* [slots][heads][vdim][dim] recurrent state per sequence (column of a value channel contiguous) */
     float *conv_tail;              /* [slots][conv_taps - 1][2 kv_heads*dim + heads*vdim] last projected inputs per sequence */
 } lm_b200_layer;

@@ -4,7 +4,7 @@ TEST INFRASTRUCTURE ONLY - see oracle/__init__.py.
 
 PINNED against (a) the unpatched reference functions imported from
 /root/reference by oracle/validate_against_reference.py on random grids, and
-(b) the known-answer vector of SURVEY.md Appendix C committed as
+(b) the known-answer vector committed as
 tests/golden/delay_known_answer.json.
 """
 

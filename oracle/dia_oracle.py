@@ -4,17 +4,17 @@ TEST INFRASTRUCTURE ONLY - see oracle/__init__.py.  Never imported by the
 product package.
 
 The reference (babybirdprd/dia-tts-prune) is pure PyTorch; every arithmetic op
-on its decode path is an ATen library call (SURVEY.md section 8(c)).  This file
+on its decode path is an ATen library call.  This file
 restates the *algorithm* - which ops, on which operands, in which order - as
 plain functions over a flat ``params`` dict that uses the reference's
-state_dict keys (SURVEY.md Appendix A), calling the same ATen entry points
+state_dict keys, calling the same ATen entry points
 (``torch.tensordot``, ``F.rms_norm``, ``F.scaled_dot_product_attention``,
 ``F.embedding``, ``F.silu``) so that on the same CPU it reproduces the
 reference bit for bit.
 
 PINNED: ``oracle/validate_against_reference.py`` (run in the build container,
 where /root/reference exists) imports the reference with the three hot-path
-patches of SURVEY.md Appendix B and checks this file against it: encoder
+patches and checks this file against it: encoder
 output, cross-KV, per-step logits, KV-cache contents, greedy code stream, the
 prompt/prefill path and the sampling filter.  The same script writes the
 golden fixtures under tests/golden/ that travel to the GPU box.
@@ -33,7 +33,7 @@ import torch.nn.functional as F
 
 
 # ----------------------------------------------------------------------------
-# parameter naming (dia/layers.py module registration order; SURVEY Appendix A)
+# parameter naming (dia/layers.py module registration order)
 # ----------------------------------------------------------------------------
 
 def param_names(cfg) -> list[str]:
@@ -125,7 +125,7 @@ def rope_inv_freq(head_dim: int, min_ts: int, max_ts: int) -> torch.Tensor:
 
 
 def rope(x: torch.Tensor, position: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """RotaryEmbedding.forward with patch B1 of SURVEY Appendix B: the rotation
+    """RotaryEmbedding.forward with its shape patch: the rotation
     of dia/layers.py:165-173 with theta = position * inv_freq broadcast over
     the head axis (x is [B, T, N, H], position is [B, T])."""
     pos = position.unsqueeze(-1).unsqueeze(-1)
@@ -318,7 +318,7 @@ def cfg_combine_and_mask(cfg, logits_2xCxV: torch.Tensor, cfg_scale: float) -> t
     """dia/model.py:447-478: guided = cond + s*(cond-uncond) with row0=uncond,
     row1=cond; EOS forbidden on channels>0; PAD and BOS forbidden everywhere;
     ids >= vocab masked only if vocab <= EOS+1 (false for 1028: id 1027 stays
-    legal, SURVEY Appendix C Q5)."""
+    legal)."""
     uncond, cond = logits_2xCxV[0], logits_2xCxV[1]
     out = cond + cfg_scale * (cond - uncond)
     dt = cfg.data
@@ -422,7 +422,7 @@ def finalize_codes(cfg, generated: torch.Tensor, codebook_size: int = 1024) -> t
 
 
 # ----------------------------------------------------------------------------
-# the generate loop (dia/model.py:631-846; semantics in SURVEY Appendix C)
+# the generate loop (dia/model.py:631-846)
 # ----------------------------------------------------------------------------
 
 @dataclass

@@ -7,7 +7,7 @@ fixtures it writes are committed and travel.
 
 What it does
   1. imports the reference ``dia`` package with ``dac``/``soundfile`` stubbed and
-     the hot-path patches B1-B4 of SURVEY.md Appendix B (the shipped code raises
+     the hot-path patches B1-B4 (the shipped code raises
      before the first token without them; nothing else is touched);
   2. checks ``oracle/dia_oracle.py`` and ``oracle/delay_oracle.py`` against it,
      bit for bit: parameter order, delay/revert gathers, encoder output,
@@ -37,7 +37,7 @@ GOLD = os.path.join(REPO, "tests", "golden")
 
 
 def import_reference():
-    """Reference modules with stubs + patches (SURVEY.md Appendix B shim)."""
+    """Reference modules with stubs + patches."""
     for n in ("dac", "soundfile"):
         sys.modules.setdefault(n, types.ModuleType(n))
     # the repo ships a drop-in package that is also called ``dia``: make sure the
@@ -168,7 +168,7 @@ def run_delay(ref):
         check_equal(f"build_revert_indices idx {B,T,C}", got_i, rpre[1])
         check_equal(f"revert_audio_delay {B,T,C}", delay_oracle.revert_audio_delay(x, 1025, dl, T),
                     ref.A.revert_audio_delay(xt, 1025, rpre, T))
-    # known answer (SURVEY.md Appendix C), produced by the reference right here
+    # known answer, produced by the reference right here
     B, T, C, dl = 1, 6, 3, [0, 1, 2]
     x = torch.tensor([[[10 + 30 * t + 11 * c for c in range(C)] for t in range(T)]], dtype=torch.int32)
     ap = ref.A.apply_audio_delay(x, 1025, 1026, ref.A.build_delay_indices(B, T, C, dl))

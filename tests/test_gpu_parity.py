@@ -19,7 +19,7 @@ from oracle import delay_oracle, dia_oracle as O
 pytestmark = pytest.mark.gpu
 DELAYS = [0, 8, 9, 10, 11, 12, 13, 14, 15]
 LOGIT_TOL = 2e-2          # the north-star bar
-LOGIT_TIGHT = 5e-4        # what the fp32-activation design actually achieves (SURVEY.md 8(c): ~2.4e-5)
+LOGIT_TIGHT = 5e-4        # what the fp32-activation design actually achieves (~2.4e-5)
 
 
 def test_native_library_is_loaded_and_device_is_blackwell():
@@ -658,7 +658,7 @@ def test_full_repeated_launches_do_not_hang(full_gpu):
 
 def test_live_text_only_prepare_matches_full(tiny_gpu):
     """Encoding / projecting only the valid text bytes of the conditional row (the only encoder work the decoder
-    can observe, SURVEY.md Appendix C Q7) gives the same live cross-KV entries and the same logits as the
+    can observe) gives the same live cross-KV entries and the same logits as the
     reference's full 2 x text_length computation."""
     dia, sd = tiny_gpu
     text = "[S1] Live tokens only. [S2] Same logits."
@@ -873,7 +873,7 @@ def test_tiny_prefill_kv_matches_oracle(tiny_gpu, gold_tiny):
     assert (lg.cpu() - lo).abs().max().item() < LOGIT_TIGHT
 
 
-# ---- N utterances per launch (SURVEY.md 8(f) rank 2): the tcgen05 batched step kernel -------------------------------------------
+# ---- N utterances per launch: the tcgen05 batched step kernel -------------------------------------------
 BATCH_TEXTS = ["[S1] Hello there. [S2] Hi.", "[S1] A second utterance, a little longer than the first. [S2] Yes.",
                "[S2] Third one starts with speaker two. [S1] Fine."]
 
@@ -1089,7 +1089,7 @@ def test_non_representable_fp32_checkpoint_is_rounded_once_and_consistently():
     """A real float32 (or float16) checkpoint is not bf16-representable.  The sm_100a path streams DenseGeneral kernels as
     bf16, so such kernels are rounded ONCE, in the module, with a warning - encoder, prompt prefill and decode engine
     then see the same numbers.  Against the oracle on the UNROUNDED weights the logits differ by the weight rounding
-    (bounded here by 6e-2, the reference's own bf16-regime error, SURVEY.md 8(c)); against the oracle on the rounded
+    (bounded here by 6e-2, the reference's own bf16-regime error); against the oracle on the rounded
     weights the usual tight bound holds."""
     import warnings
     from dia_tts_prune_b200 import layers as LY

@@ -24,7 +24,7 @@ def test_delay_known_answer(gold_delay):
     assert ap.tolist() == g["apply"] and ap.dtype == np.int32
     rv = delay_oracle.revert_audio_delay(ap, g["pad"], g["delay"], g["T"])
     assert rv.tolist() == g["revert"]
-    # SURVEY.md Appendix C, verbatim
+    # verbatim
     assert ap[0, :, 1].tolist() == [1026, 21, 51, 81, 111, 141]
     assert ap[0, :, 2].tolist() == [1026, 1026, 32, 62, 92, 122]
     assert rv[0, :, 2].tolist() == [32, 62, 92, 122, 122, 122]
@@ -167,7 +167,7 @@ def test_oracle_full_size_two_steps_against_golden(gold_full):
     for s in (1, 2):
         assert np.abs(tr.logits[s].numpy() - gold_full["logits"][steps.index(s)]).max() < 1e-4
     assert torch.equal(tr.codes, torch.from_numpy(gold_full["codes"][: tr.codes.shape[0]]))
-    assert gold_full["margins"].min() > 3e-4                       # the seed screen (SURVEY.md 8(d))
+    assert gold_full["margins"].min() > 3e-4                       # the seed screen
 
 
 def test_effective_text_and_text_encoding():
