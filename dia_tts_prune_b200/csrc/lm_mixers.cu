@@ -164,10 +164,10 @@ talk_prep_kernel(float* __restrict__ proj, int ld, const float* __restrict__ bia
 // segment, segments are walked one after the other and a row's statistics move only while its own segment is walked.
 // With gridDim.y > 1 (TQ == 1, decoding) every CTA takes a share of the row's keys, writes {maximum, denominator,
 // sums[vdim]} per head, and the CTA that arrives last merges the shares in their fixed order and adds the sink.
-constexpr int kTalkThreads = 256, kTalkWarps = kTalkThreads / 32, kTalkTK = 64;
+constexpr int kTalkTK = 64;
 
-template <int VU, int NP>
-__global__ void __launch_bounds__(kTalkThreads, 1)
+template <int VU, int NP, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gate_off, const float* __restrict__ kcache,
                       const float* __restrict__ vcache, const int* __restrict__ table, int max_pages, int page_size, int H,
                       int G, int dim, int vdim, const float* __restrict__ talk, const float* __restrict__ sink,
@@ -176,7 +176,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                       unsigned* __restrict__ arrived) {
     extern __shared__ __align__(16) float sm[];
     __shared__ bool is_last;
-    constexpr int TK = kTalkTK;
+    constexpr int TK = kTalkTK, NT = NW * 32;
     const int D4 = (dim + 3) >> 2, DQ = 4 * D4 + 4, SV = (vdim + 3) & ~3, kv_stride = max(DQ, SV);
     const int n_pairs = H * TQ, rep = H / G;
     float* Qs = sm;                                           // [n_pairs][DQ]
@@ -201,8 +201,8 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         s_slot[tid] = tid < n_rows ? row_slot[r0 + tid] : -1;
         s_pos[tid] = tid < n_rows ? row_pos[r0 + tid] : -1;
     }
-    for (int i = tid; i < H * H; i += kTalkThreads) Tm[i] = talk ? talk[i] : (i / H == i % H ? 1.f : 0.f);
-    for (int idx = tid; idx < n_pairs * D4; idx += kTalkThreads) {
+    for (int i = tid; i < H * H; i += NT) Tm[i] = talk ? talk[i] : (i / H == i % H ? 1.f : 0.f);
+    for (int idx = tid; idx < n_pairs * D4; idx += NT) {
         const int p = idx / D4, c = (idx - p * D4) * 4, h = p / TQ, i = p - h * TQ;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n_rows) {
@@ -217,7 +217,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         }
         *reinterpret_cast<float4*>(Qs + (size_t)p * DQ + c) = v;
     }
-    for (int p = tid; p < n_pairs; p += kTalkThreads) {
+    for (int p = tid; p < n_pairs; p += NT) {
         m_s[p] = (S == 1 && sink) ? sink[p / TQ] : -CUDART_INF_F;
         l_s[p] = 0.f;
     }
@@ -228,7 +228,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     int pg[NP];                                               // key/value head of owned pair n (-1: none)
 #pragma unroll
     for (int n = 0; n < NP; ++n) {
-        const int p = warp + kTalkWarps * n;
+        const int p = warp + NW * n;
         pg[n] = p < n_pairs ? (p / TQ) / rep : -1;
 #pragma unroll
         for (int u = 0; u < VU; ++u) acc[n][u] = 0.f;
@@ -257,7 +257,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
             const float* cache = is_k ? kcache : vcache;
             const bool vec = is_k ? vec_k : vec_v;
             float* dstb = KVs + (stg & 1) * TK * kv_stride;
-            for (int idx = tid; idx < TK * W4; idx += kTalkThreads) {
+            for (int idx = tid; idx < TK * W4; idx += NT) {
                 const int jj = idx / W4, c = (idx - jj * W4) * 4, j = j0 + jj;
                 float* dst = dstb + jj * kv_stride + c;
                 const bool in = jj < jn;
@@ -295,10 +295,10 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                 const int np_g = rep * TQ;
                 const float* Qg = Qs + (size_t)g * np_g * DQ;
                 float* Rg = Rs + g * np_g * TK;
-                if (np_g >= 32) {                             // 4 pairs x 2 keys per thread
+                if (np_g >= 32 && ((np_g + 3) / 4) * 2 > NW) {    // 4 pairs x 2 keys per thread
                     const float* k0p = KV + lane * kv_stride;
                     const float* k1p = KV + (lane + 32) * kv_stride;
-                    for (int ch = warp; ch * 4 < np_g; ch += kTalkWarps) {
+                    for (int ch = warp; ch * 4 < np_g; ch += NW) {
                         const float* qp[4];
 #pragma unroll
                         for (int a = 0; a < 4; ++a) qp[a] = Qg + (size_t)min(ch * 4 + a, np_g - 1) * DQ;
@@ -323,8 +323,30 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                                 Rg[(ch * 4 + a) * TK + lane + 32] = a1[a];
                             }
                     }
+                } else if (np_g >= 32) {                      // fewer 4-pair chunks than half the warps: 4 pairs x 1 key
+                    for (int it = warp; it * 2 < np_g; it += NW) {    // items: (chunk of 4 pairs, half of the keys)
+                        const int ch = it >> 1, jj = lane + 32 * (it & 1);
+                        const float* kp = KV + jj * kv_stride;
+                        const float* qp[4];
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) qp[a] = Qg + (size_t)min(ch * 4 + a, np_g - 1) * DQ;
+                        float a0[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+                        for (int d4 = 0; d4 < D4; ++d4) {
+                            const float4 k0 = *reinterpret_cast<const float4*>(kp + 4 * d4);
+#pragma unroll
+                            for (int a = 0; a < 4; ++a) {
+                                const float4 q = *reinterpret_cast<const float4*>(qp[a] + 4 * d4);
+                                a0[a] = fmaf(q.x, k0.x, a0[a]); a0[a] = fmaf(q.y, k0.y, a0[a]);
+                                a0[a] = fmaf(q.z, k0.z, a0[a]); a0[a] = fmaf(q.w, k0.w, a0[a]);
+                            }
+                        }
+#pragma unroll
+                        for (int a = 0; a < 4; ++a)
+                            if (ch * 4 + a < np_g) Rg[(ch * 4 + a) * TK + jj] = a0[a];
+                    }
                 } else {                                      // few pairs (decoding): 1 pair x 1 key per thread
-                    for (int it = warp; it < 2 * np_g; it += kTalkWarps) {
+                    for (int it = warp; it < 2 * np_g; it += NW) {
                         const int lp = it >> 1, jj = lane + 32 * (it & 1);
                         const float* qp = Qg + (size_t)lp * DQ;
                         const float* kp = KV + jj * kv_stride;
@@ -342,7 +364,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                 if (ph < G - 1) continue;
                 __syncthreads();                              // the raw scores of all heads are there
                 // ---- B: mix across heads, mask, online softmax ----
-                for (int p = warp; p < n_pairs; p += kTalkWarps) {
+                for (int p = warp; p < n_pairs; p += NW) {
                     const int h = p / TQ, i = p - h * TQ;
                     const bool live = i >= seg_a && i < seg_b;
                     const int qi = s_pos[i];
@@ -387,40 +409,57 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 #pragma unroll
             for (int n = 0; n < NP; ++n)
                 if (pg[n] == g) {
-                    const float c = c_s[warp + kTalkWarps * n];
+                    const float c = c_s[warp + NW * n];
 #pragma unroll
                     for (int u = 0; u < VU; ++u) acc[n][u] *= c;
                 }
-            for (int j = 0; j < jn4; j += 4) {
-                float v[4][VU];
+            // the pairs of one key/value head are neighbours in a warp's list: two at a time share the loaded values
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj)
+            for (int n0 = 0; n0 < NP; n0 += 2) {
+                const bool own0 = pg[n0] == g, own1 = n0 + 1 < NP && pg[n0 + 1 < NP ? n0 + 1 : n0] == g;
+                if (!own0 && !own1) continue;
+                const float* P0 = Ps + (warp + NW * n0) * TK;
+                const float* P1 = Ps + (warp + NW * (n0 + 1 < NP ? n0 + 1 : n0)) * TK;
+                for (int j = 0; j < jn4; j += 4) {
+                    float v[4][VU];
 #pragma unroll
-                    for (int u = 0; u < VU; u += VW) {
-                        const int col = col_of(u);
-                        const float* src = KV + (j + jj) * kv_stride + col;
-                        if (VW == 4) {
-                            const float4 t = col < SV ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
-                            v[jj][u] = t.x; v[jj][u + 1] = t.y; v[jj][u + 2] = t.z; v[jj][u + 3] = t.w;
-                        } else if (VW == 2) {
-                            const float2 t = col < SV ? *reinterpret_cast<const float2*>(src) : make_float2(0.f, 0.f);
-                            v[jj][u] = t.x; v[jj][u + 1] = t.y;
-                        } else {
-                            v[jj][u] = col < SV ? *src : 0.f;
+                    for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+                        for (int u = 0; u < VU; u += VW) {
+                            const int col = col_of(u);
+                            const float* src = KV + (j + jj) * kv_stride + col;
+                            if (VW == 4) {
+                                const float4 t = col < SV ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                v[jj][u] = t.x; v[jj][u + 1] = t.y; v[jj][u + 2] = t.z; v[jj][u + 3] = t.w;
+                            } else if (VW == 2) {
+                                const float2 t = col < SV ? *reinterpret_cast<const float2*>(src) : make_float2(0.f, 0.f);
+                                v[jj][u] = t.x; v[jj][u + 1] = t.y;
+                            } else {
+                                v[jj][u] = col < SV ? *src : 0.f;
+                            }
                         }
-                    }
-#pragma unroll
-                for (int n = 0; n < NP; ++n)
-                    if (pg[n] == g) {
-                        const float4 pj = *reinterpret_cast<const float4*>(Ps + (warp + kTalkWarps * n) * TK + j);
+                    if (own0) {
+                        const float4 pj = *reinterpret_cast<const float4*>(P0 + j);
 #pragma unroll
                         for (int u = 0; u < VU; ++u) {
-                            acc[n][u] = fmaf(pj.x, v[0][u], acc[n][u]);
-                            acc[n][u] = fmaf(pj.y, v[1][u], acc[n][u]);
-                            acc[n][u] = fmaf(pj.z, v[2][u], acc[n][u]);
-                            acc[n][u] = fmaf(pj.w, v[3][u], acc[n][u]);
+                            acc[n0][u] = fmaf(pj.x, v[0][u], acc[n0][u]);
+                            acc[n0][u] = fmaf(pj.y, v[1][u], acc[n0][u]);
+                            acc[n0][u] = fmaf(pj.z, v[2][u], acc[n0][u]);
+                            acc[n0][u] = fmaf(pj.w, v[3][u], acc[n0][u]);
                         }
                     }
+                    if (own1) {
+                        const float4 pj = *reinterpret_cast<const float4*>(P1 + j);
+#pragma unroll
+                        for (int u = 0; u < VU; ++u) {
+                            float& dst = acc[n0 + 1 < NP ? n0 + 1 : n0][u];
+                            dst = fmaf(pj.x, v[0][u], dst);
+                            dst = fmaf(pj.y, v[1][u], dst);
+                            dst = fmaf(pj.z, v[2][u], dst);
+                            dst = fmaf(pj.w, v[3][u], dst);
+                        }
+                    }
+                }
             }
         }
         seg_a = seg_b;
@@ -431,7 +470,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 #pragma unroll
         for (int n = 0; n < NP; ++n) {
             if (pg[n] < 0) continue;
-            const int p = warp + kTalkWarps * n, h = p / TQ, i = p - h * TQ;
+            const int p = warp + NW * n, h = p / TQ, i = p - h * TQ;
             if (i >= n_rows) continue;
             float l = l_s[p];
             if (sink) l += expf(sink[h] - m_s[p]);
@@ -455,7 +494,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 #pragma unroll
     for (int n = 0; n < NP; ++n) {
         if (pg[n] < 0) continue;
-        const int p = warp + kTalkWarps * n;                  // TQ == 1: the pair is the head
+        const int p = warp + NW * n;                  // TQ == 1: the pair is the head
         float* dst = part + (((size_t)r0 * H + p) * S + sp) * stride;
         if (lane == 0) { dst[0] = m_s[p]; dst[1] = l_s[p]; }
 #pragma unroll
@@ -474,7 +513,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int h = warp; h < H; h += kTalkWarps) {
+    for (int h = warp; h < H; h += NW) {
         const float* src = part + ((size_t)r0 * H + h) * S * stride;
         const float ms = lane < S ? __ldcg(src + lane * stride) : -CUDART_INF_F;
         const float ls = lane < S ? __ldcg(src + lane * stride + 1) : 0.f;
@@ -800,7 +839,7 @@ static size_t talk_smem(const TalkShape& a, int TQ) {
            2 * (size_t)TQ * 4;
 }
 
-template <int VU, int NP>
+template <int VU, int NP, int NW>
 static cudaError_t launch_talk_inst(const float* proj, int ld, int q_off, int gate_off, const float* kcache, const float* vcache,
                                     const PageMap& pm, const TalkShape& a, const RowMeta& rm, float* out, int ldo,
                                     __nv_bfloat16* out_b, float* part, unsigned* arrived, int M, int TQ, int S, cudaStream_t st) {
@@ -810,47 +849,54 @@ static cudaError_t launch_talk_inst(const float* proj, int ld, int q_off, int ga
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || allowed[dev] < smem) {
-        e = cudaFuncSetAttribute(talk_attention_kernel<VU, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(talk_attention_kernel<VU, NP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) allowed[dev] = smem;
     }
-    return launch_pdl(talk_attention_kernel<VU, NP>, dim3((M + TQ - 1) / TQ, S), dim3(kTalkThreads), smem, st, proj, ld, q_off,
+    return launch_pdl(talk_attention_kernel<VU, NP, NW>, dim3((M + TQ - 1) / TQ, S), dim3(NW * 32), smem, st, proj, ld, q_off,
                       gate_off, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.vdim, a.talk,
                       a.sink, rm.slot, rm.pos, out, ldo, out_b, M, TQ, part, arrived);
 }
 
-// the most pairs (heads x rows of a tile) a CTA carries: 8 warps x 16 pairs, 8 x 8 with values wider than 128
+// the most pairs (heads x rows of a tile) a CTA carries: 128, 64 with values wider than 128 (accumulators per thread)
 static int talk_max_pairs(int vdim) { return vdim > 128 ? 64 : 128; }
 
 bool talk_attention_supported(const TalkShape& a) {
     return a.heads > 0 && a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.dim > 0 && a.vdim > 0 && a.vdim <= 256 &&
-           a.heads <= talk_max_pairs(a.vdim) && a.heads <= 32 * kTalkWarps && talk_smem(a, 1) <= 200 * 1024;
+           a.heads <= talk_max_pairs(a.vdim) && talk_smem(a, 1) <= 200 * 1024;
 }
 
-// split_ws: kAttnRowsKernelMax * heads * kAttnSplitsMax * (vdim + 2) floats; arrived: kAttnRowsKernelMax zeroed counters
+// split_ws: kAttnRowsKernelMax * heads * kAttnSplitsMax * (vdim + 2) floats; arrived: kAttnRowsKernelMax zeroed counters.
+// Prompt portions run 16 warps per CTA (up to 8 pairs per warp: half the accumulators of an 8-warp CTA, twice the warps
+// to hide the latencies of a tile's dependent phases); a handful of rows run 8 warps per (row, share of the keys).
 cudaError_t launch_talk_attention(const float* proj, int ld, int q_off, int gate_off, const float* kcache, const float* vcache,
                                   const PageMap& pm, const TalkShape& a, const RowMeta& rm, float* out, int ldo, void* out_bf16,
                                   float* split_ws, unsigned* arrived, int M, cudaStream_t st) {
     if (!talk_attention_supported(a)) return cudaErrorNotSupported;
-    int TQ = 1, S = 1;
-    if (M > kAttnRowsKernelMax) {
-        TQ = 16;
-        while (TQ > 1 && (a.heads * TQ > talk_max_pairs(a.vdim) || talk_smem(a, TQ) > 200 * 1024)) TQ >>= 1;
-    } else {
-        // enough CTAs for two per SM, at least one key tile per share
-        const long long max_keys = (long long)pm.max_pages * pm.page_size;
-        S = (2 * 148 + M - 1) / M;
-        S = (int)std::max<long long>(1, std::min<long long>(std::min(S, kAttnSplitsMax), (max_keys + kTalkTK - 1) / kTalkTK));
-    }
     __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(out_bf16);
-    const int np = (a.heads * TQ + kTalkWarps - 1) / kTalkWarps, vu = (a.vdim + 31) / 32;
-#define TALK_CASE(VU, NP) \
-    return launch_talk_inst<VU, NP>(proj, ld, q_off, gate_off, kcache, vcache, pm, a, rm, out, ldo, ob, split_ws, arrived, M, TQ, S, st)
-    if (vu <= 1) { if (np <= 4) TALK_CASE(1, 4); TALK_CASE(1, 16); }
-    if (vu <= 2) { if (np <= 4) TALK_CASE(2, 4); TALK_CASE(2, 16); }
-    if (vu <= 4) { if (np <= 4) TALK_CASE(4, 4); TALK_CASE(4, 16); }
-    if (np <= 4) TALK_CASE(8, 4);
-    TALK_CASE(8, 8);
+    const int vu = (a.vdim + 31) / 32;
+#define TALK_CASE(VU, NP, NW) \
+    return launch_talk_inst<VU, NP, NW>(proj, ld, q_off, gate_off, kcache, vcache, pm, a, rm, out, ldo, ob, split_ws, arrived, M, TQ, S, st)
+    if (M > kAttnRowsKernelMax) {
+        int TQ = 16;
+        const int S = 1;
+        while (TQ > 1 && (a.heads * TQ > talk_max_pairs(a.vdim) || talk_smem(a, TQ) > 200 * 1024)) TQ >>= 1;
+        if (vu <= 1) TALK_CASE(1, 8, 16);
+        if (vu <= 2) TALK_CASE(2, 8, 16);
+        if (vu <= 4) TALK_CASE(4, 8, 16);
+        TALK_CASE(8, 4, 16);
+    }
+    // enough CTAs for two per SM, at least one key tile per share
+    const int TQ = 1;
+    const long long max_keys = (long long)pm.max_pages * pm.page_size;
+    int S = (2 * 148 + M - 1) / M;
+    S = (int)std::max<long long>(1, std::min<long long>(std::min(S, kAttnSplitsMax), (max_keys + kTalkTK - 1) / kTalkTK));
+    const int np = (a.heads + 7) / 8;
+    if (vu <= 1) { if (np <= 4) TALK_CASE(1, 4, 8); TALK_CASE(1, 16, 8); }
+    if (vu <= 2) { if (np <= 4) TALK_CASE(2, 4, 8); TALK_CASE(2, 16, 8); }
+    if (vu <= 4) { if (np <= 4) TALK_CASE(4, 4, 8); TALK_CASE(4, 16, 8); }
+    if (np <= 4) TALK_CASE(8, 4, 8);
+    TALK_CASE(8, 8, 8);
 #undef TALK_CASE
 }
 
