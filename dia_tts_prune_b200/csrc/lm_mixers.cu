@@ -178,7 +178,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     __shared__ bool is_last;
     constexpr int TK = kTalkTK, NT = NW * 32;
     const int D4 = (dim + 3) >> 2, DQ = 4 * D4 + 4, SV = (vdim + 3) & ~3, kv_stride = max(DQ, SV);
-    const int n_pairs = H * TQ, rep = H / G;
+    const int n_pairs = H * TQ, rep = H / G, tq_shift = 31 - __clz(TQ);       // TQ is a power of two
     float* Qs = sm;                                           // [n_pairs][DQ]
     float* KVs = Qs + (size_t)n_pairs * DQ;                   // [2][TK][kv_stride]: key and value tiles, double-buffered
     float* Rs = KVs + 2 * TK * kv_stride;                     // [n_pairs][TK] raw scores
@@ -203,7 +203,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     }
     for (int i = tid; i < H * H; i += NT) Tm[i] = talk ? talk[i] : (i / H == i % H ? 1.f : 0.f);
     for (int idx = tid; idx < n_pairs * D4; idx += NT) {
-        const int p = idx / D4, c = (idx - p * D4) * 4, h = p / TQ, i = p - h * TQ;
+        const int p = idx / D4, c = (idx - p * D4) * 4, h = p >> tq_shift, i = p & (TQ - 1);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n_rows) {
             const float* src = proj + (size_t)(r0 + i) * ld + q_off + (size_t)h * dim + c;
@@ -218,7 +218,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         *reinterpret_cast<float4*>(Qs + (size_t)p * DQ + c) = v;
     }
     for (int p = tid; p < n_pairs; p += NT) {
-        m_s[p] = (S == 1 && sink) ? sink[p / TQ] : -CUDART_INF_F;
+        m_s[p] = (S == 1 && sink) ? sink[p >> tq_shift] : -CUDART_INF_F;
         l_s[p] = 0.f;
     }
     // value columns of a lane: VW consecutive ones per group of 32 * VW columns (vector loads of the value tile)
@@ -229,7 +229,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 #pragma unroll
     for (int n = 0; n < NP; ++n) {
         const int p = warp + NW * n;
-        pg[n] = p < n_pairs ? (p / TQ) / rep : -1;
+        pg[n] = p < n_pairs ? (p >> tq_shift) / rep : -1;
 #pragma unroll
         for (int u = 0; u < VU; ++u) acc[n][u] = 0.f;
     }
@@ -250,31 +250,44 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         // s lives in buffer s & 1; the gather of stage s + 1 is issued (asynchronous 16-byte copies, zero-filled beyond
         // the last key) before stage s is computed, so a stage's loads fly during the arithmetic of the one before.
         const int n_stage = k_begin < k_end ? ((k_end - k_begin + TK - 1) / TK) * 2 * G : 0;
+        // a thread copies rows warp, warp + NW, ... of a tile and the 16-byte columns lane, lane + 32, ...; where a row
+        // lives ((page * G) * page_size + offset in the page) is looked up once per tile, at its first stage
+        int rowpg[TK / NW];
         auto gather = [&](int stg) {
             const int tile = stg / (2 * G), ph = stg - tile * 2 * G, j0 = k_begin + tile * TK, jn = min(TK, k_end - j0);
+            if (ph == 0) {
+#pragma unroll
+                for (int i = 0; i < TK / NW; ++i) {
+                    const int jj = warp + NW * i, j = j0 + jj;
+                    rowpg[i] = jj < jn ? pages[j / page_size] * G * page_size + (j % page_size) : -1;
+                }
+            }
             const bool is_k = ph < G;
             const int g = is_k ? ph : ph - G, width = is_k ? dim : vdim, W4 = is_k ? D4 : (SV >> 2);
             const float* cache = is_k ? kcache : vcache;
             const bool vec = is_k ? vec_k : vec_v;
             float* dstb = KVs + (stg & 1) * TK * kv_stride;
-            for (int idx = tid; idx < TK * W4; idx += NT) {
-                const int jj = idx / W4, c = (idx - jj * W4) * 4, j = j0 + jj;
-                float* dst = dstb + jj * kv_stride + c;
-                const bool in = jj < jn;
-                const float* src = cache + (in ? (((size_t)pages[j / page_size] * G + g) * page_size + (j % page_size)) * width + c : 0);
-                if (vec) {
-                    const unsigned d32 = (unsigned)__cvta_generic_to_shared(dst);
-                    const int bytes = in ? 16 : 0;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d32), "l"(src), "r"(bytes) : "memory");
-                } else {
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (in) {
-                        v.x = src[0];
-                        if (c + 1 < width) v.y = src[1];
-                        if (c + 2 < width) v.z = src[2];
-                        if (c + 3 < width) v.w = src[3];
+            for (int c4 = lane; c4 < W4; c4 += 32) {
+                const int c = c4 * 4;
+#pragma unroll
+                for (int i = 0; i < TK / NW; ++i) {
+                    float* dst = dstb + (warp + NW * i) * kv_stride + c;
+                    const bool in = rowpg[i] >= 0;
+                    const float* src = cache + (in ? ((size_t)rowpg[i] + (size_t)g * page_size) * width + c : 0);
+                    if (vec) {
+                        const unsigned d32 = (unsigned)__cvta_generic_to_shared(dst);
+                        const int bytes = in ? 16 : 0;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d32), "l"(src), "r"(bytes) : "memory");
+                    } else {
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (in) {
+                            v.x = src[0];
+                            if (c + 1 < width) v.y = src[1];
+                            if (c + 2 < width) v.z = src[2];
+                            if (c + 3 < width) v.w = src[3];
+                        }
+                        *reinterpret_cast<float4*>(dst) = v;
                     }
-                    *reinterpret_cast<float4*>(dst) = v;
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -365,7 +378,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                 __syncthreads();                              // the raw scores of all heads are there
                 // ---- B: mix across heads, mask, online softmax ----
                 for (int p = warp; p < n_pairs; p += NW) {
-                    const int h = p / TQ, i = p - h * TQ;
+                    const int h = p >> tq_shift, i = p & (TQ - 1);
                     const bool live = i >= seg_a && i < seg_b;
                     const int qi = s_pos[i];
                     float s[2];
@@ -470,7 +483,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 #pragma unroll
         for (int n = 0; n < NP; ++n) {
             if (pg[n] < 0) continue;
-            const int p = warp + NW * n, h = p / TQ, i = p - h * TQ;
+            const int p = warp + NW * n, h = p >> tq_shift, i = p & (TQ - 1);
             if (i >= n_rows) continue;
             float l = l_s[p];
             if (sink) l += expf(sink[h] - m_s[p]);
